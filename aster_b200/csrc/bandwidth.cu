@@ -1,0 +1,222 @@
+// HBM-bound kernels of the hot path: vector_add, copy_2d_padded, add_relu.
+//
+// All three move 16 bytes per thread per access (128-bit loads/stores, fully coalesced: one
+// warp touches 512 contiguous bytes), keep several independent loads in flight per thread, and
+// run as persistent grid-stride kernels sized to a multiple of the SM count.  Loads bypass L1
+// allocation (`ld.global.nc.L1::no_allocate`) and stores are streaming (`st.global.cs`): every
+// byte is touched exactly once, so caching it would only evict useful lines.
+//
+// Algorithmic bytes per element: vector_add / add_relu 12 (two 4-byte reads, one write);
+// copy 8.
+#include "common.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCtasPerSm = 8;
+
+template <typename V>
+__device__ __forceinline__ V ld_stream(const V* p) {
+  static_assert(sizeof(V) == 16, "16-byte vectors only");
+  int4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return *reinterpret_cast<V*>(&r);
+}
+
+template <typename V>
+__device__ __forceinline__ void st_stream(V* p, V v) {
+  static_assert(sizeof(V) == 16, "16-byte vectors only");
+  int4 r = *reinterpret_cast<int4*>(&v);
+  asm volatile("st.global.cs.v4.s32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w)
+               : "memory");
+}
+
+struct AddI32 {
+  using T = int32_t;
+  using V = int4;
+  // Wrapping add, like v_add_u32 in the reference kernel.
+  static __device__ __forceinline__ T op(T a, T b) {
+    return static_cast<T>(static_cast<uint32_t>(a) + static_cast<uint32_t>(b));
+  }
+};
+struct AddF32 {
+  using T = float;
+  using V = float4;
+  static __device__ __forceinline__ T op(T a, T b) { return __fadd_rn(a, b); }
+};
+struct AddReluF32 {
+  using T = float;
+  using V = float4;
+  // v_add_f32 then v_max_f32 with 0 (examples/07_simple_fusion/pin-fusion-asm.mlir:34-62).
+  static __device__ __forceinline__ T op(T a, T b) { return fmaxf(__fadd_rn(a, b), 0.0f); }
+};
+
+template <typename Op>
+__device__ __forceinline__ typename Op::V apply4(typename Op::V a, typename Op::V b) {
+  typename Op::V c;
+  c.x = Op::op(a.x, b.x);
+  c.y = Op::op(a.y, b.y);
+  c.z = Op::op(a.z, b.z);
+  c.w = Op::op(a.w, b.w);
+  return c;
+}
+
+// Elementwise c = op(a, b) over n elements.  `UNROLL` 16-byte vectors per input per thread are
+// loaded before any is consumed.  Requires 16-byte aligned pointers; the last n % 4 elements
+// are handled by the first threads of the grid.
+template <typename Op, int UNROLL>
+__global__ void __launch_bounds__(kThreads) elementwise_vec_kernel(const typename Op::T* __restrict__ a,
+                                                                  const typename Op::T* __restrict__ b,
+                                                                  typename Op::T* __restrict__ c, size_t n) {
+  using V = typename Op::V;
+  const size_t nvec = n / 4;
+  const V* av = reinterpret_cast<const V*>(a);
+  const V* bv = reinterpret_cast<const V*>(b);
+  V* cv = reinterpret_cast<V*>(c);
+  const size_t chunk = static_cast<size_t>(kThreads) * UNROLL;
+  const size_t nchunks = nvec / chunk;
+  for (size_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
+    const size_t base = ch * chunk + threadIdx.x;
+    V ra[UNROLL], rb[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) ra[u] = ld_stream(av + base + u * kThreads);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) rb[u] = ld_stream(bv + base + u * kThreads);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) st_stream(cv + base + u * kThreads, apply4<Op>(ra[u], rb[u]));
+  }
+  // Vector remainder (fewer than one chunk) and scalar tail.
+  const size_t gtid = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const size_t gsz = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t v = nchunks * chunk + gtid; v < nvec; v += gsz) st_stream(cv + v, apply4<Op>(ld_stream(av + v), ld_stream(bv + v)));
+  for (size_t i = nvec * 4 + gtid; i < n; i += gsz) c[i] = Op::op(a[i], b[i]);
+}
+
+// Fallback for pointers that are not 16-byte aligned: 4-byte accesses, still coalesced.
+template <typename Op>
+__global__ void __launch_bounds__(kThreads) elementwise_scalar_kernel(const typename Op::T* __restrict__ a,
+                                                                     const typename Op::T* __restrict__ b,
+                                                                     typename Op::T* __restrict__ c, size_t n) {
+  const size_t gsz = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += gsz) c[i] = Op::op(a[i], b[i]);
+}
+
+int sm_count() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename Op>
+int launch_elementwise(const typename Op::T* a, const typename Op::T* b, typename Op::T* c, size_t n, void* stream,
+                       const char* what) {
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(a && b && c, "%s: NULL pointer", what);
+  constexpr int UNROLL = 4;
+  const size_t per_cta = static_cast<size_t>(kThreads) * UNROLL * 4;
+  size_t want = (n + per_cta - 1) / per_cta;
+  const size_t cap = static_cast<size_t>(sm_count()) * kCtasPerSm;
+  const int grid = static_cast<int>(want < cap ? (want ? want : 1) : cap);
+  if (aligned16(a) && aligned16(b) && aligned16(c)) {
+    elementwise_vec_kernel<Op, UNROLL><<<grid, kThreads, 0, b200::as_stream(stream)>>>(a, b, c, n);
+  } else {
+    elementwise_scalar_kernel<Op><<<grid, kThreads, 0, b200::as_stream(stream)>>>(a, b, c, n);
+  }
+  b200::count_launch();
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+// dst[r, c] = src[r, c] for r < M, c < N; both row-major with pitch N, N % 4 == 0.
+//
+// Work item = (row, column tile of kThreads*4 columns): the reference's (row, 256-column tile)
+// per 64-lane wave (examples/06_copy_layout/copy_2d_padded.py:46-55) widened to a 256-thread
+// CTA.  Items are dealt to the persistent CTAs in groups of DEPTH consecutive items, group g
+// to CTA g % num_ctas (the reference deals single items the same way, :74-76), and all DEPTH
+// loads of a group are issued before its first store, which is the reference's `depth`
+// software pipelining (:71-96).  A lane whose column is >= N neither loads nor stores: the
+// per-dimension out-of-bounds rule the reference gets from buffer descriptors.
+template <int DEPTH>
+__global__ void __launch_bounds__(kThreads) copy_2d_padded_kernel(const float* __restrict__ src,
+                                                                 float* __restrict__ dst, long long M, long long N,
+                                                                 unsigned n_col_tiles, unsigned long long n_items) {
+  constexpr int kTileN = kThreads * 4;
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * DEPTH;
+  for (unsigned long long first = static_cast<unsigned long long>(blockIdx.x) * DEPTH; first < n_items; first += stride) {
+    float4 v[DEPTH];
+    long long off[DEPTH];
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      const unsigned long long item = first + d;
+      off[d] = -1;
+      if (item < n_items) {
+        const unsigned long long row = item / n_col_tiles;
+        const unsigned ct = static_cast<unsigned>(item - row * n_col_tiles);
+        const long long col = static_cast<long long>(ct) * kTileN + threadIdx.x * 4;
+        if (col < N) off[d] = static_cast<long long>(row) * N + col;
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d)
+      if (off[d] >= 0) v[d] = ld_stream(reinterpret_cast<const float4*>(src + off[d]));
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d)
+      if (off[d] >= 0) st_stream(reinterpret_cast<float4*>(dst + off[d]), v[d]);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_vector_add_i32(const int32_t* a, const int32_t* b, int32_t* c, size_t n, void* stream) {
+  return launch_elementwise<AddI32>(a, b, c, n, stream, "vector_add_i32");
+}
+
+int b200_vector_add_f32(const float* a, const float* b, float* c, size_t n, void* stream) {
+  return launch_elementwise<AddF32>(a, b, c, n, stream, "vector_add_f32");
+}
+
+int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void* stream) {
+  return launch_elementwise<AddReluF32>(a, b, out, n, stream, "add_relu_f32");
+}
+
+int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, int depth, int num_ctas,
+                            void* stream) {
+  B200_REQUIRE(M >= 0 && N >= 0, "copy_2d_padded: negative extent %lld x %lld", (long long)M, (long long)N);
+  // Same precondition as the reference: a 16-byte access must not straddle the end of a row.
+  B200_REQUIRE(N % 4 == 0, "copy_2d_padded: N=%lld must be a multiple of 4", (long long)N);
+  B200_REQUIRE(depth >= 1 && depth <= 8, "copy_2d_padded: depth=%d outside [1,8]", depth);
+  B200_REQUIRE(num_ctas >= 0, "copy_2d_padded: num_ctas=%d is negative", num_ctas);
+  if (M == 0 || N == 0) return B200_OK;
+  B200_REQUIRE(src && dst, "copy_2d_padded: NULL pointer");
+  B200_REQUIRE(aligned16(src) && aligned16(dst), "copy_2d_padded: pointers must be 16-byte aligned");
+  constexpr int kTileN = kThreads * 4;
+  const unsigned long long n_col_tiles = (static_cast<unsigned long long>(N) + kTileN - 1) / kTileN;
+  B200_REQUIRE(n_col_tiles < (1ull << 32), "copy_2d_padded: N too large");
+  const unsigned long long n_items = static_cast<unsigned long long>(M) * n_col_tiles;
+  // Round depth up to the instantiated pipeline depths {1,2,4,8}.
+  int d = 1;
+  while (d < depth) d *= 2;
+  unsigned long long want = (n_items + d - 1) / d;
+  unsigned long long cap = num_ctas > 0 ? static_cast<unsigned long long>(num_ctas)
+                                        : static_cast<unsigned long long>(sm_count()) * kCtasPerSm;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  cudaStream_t s = b200::as_stream(stream);
+  const unsigned nct = static_cast<unsigned>(n_col_tiles);
+  switch (d) {
+    case 1: copy_2d_padded_kernel<1><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
+    case 2: copy_2d_padded_kernel<2><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
+    case 4: copy_2d_padded_kernel<4><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
+    default: copy_2d_padded_kernel<8><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
+  }
+  b200::count_launch();
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,531 @@
+// GEMM half of the aster_b200 C ABI: plan (kernel selection + validation), run, timing loops,
+// B packing for the direct-B path, and the L2 flush.
+//
+// A "plan" plays the role of the reference's compiled artifact + loaded module
+// (compile_multitile_gemm / GpuModule, test_102_gemm_python_multitile_lds_cdna3.py:391-414):
+// everything that depends only on the problem description is decided once; pointers arrive
+// with each run, exactly like the 3-pointer kernarg ABI of the reference kernel (:148-151).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "common.h"
+#include "gemm_kernel.cuh"
+
+namespace {
+
+using gemm::Params;
+
+// ---------------------------------------------------------------------------------------------
+// cuTensorMapEncodeTiled, resolved through the runtime so that the library has no link-time
+// dependency on libcuda (it must load on machines without a driver).
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    cudaGetLastError();
+  });
+  return fn;
+}
+
+// Row-major [rows, cols] matrix of `elt_bytes`-wide elements, tiled in boxes of
+// box_rows x (128 bytes of columns), written to shared memory with the 128-byte swizzle.
+// Out-of-range parts of a box read as zero, which is what makes ragged M, N and K safe.
+int make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return b200::fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMapDataType dt;
+  uint32_t eb;
+  switch (dtype) {
+    case B200_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; eb = 2; break;
+    case B200_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; eb = 2; break;
+    default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; eb = 1; break;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * eb};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(gemm::kRowBytes / eb), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return b200::fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu box_rows=%u)",
+                      static_cast<int>(r), (unsigned long long)rows, (unsigned long long)cols, box_rows);
+  }
+  return B200_OK;
+}
+
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const Params);
+
+KernelFn select_kernel(int bn, int dtype_c) {
+  const bool f32 = dtype_c == B200_F32;
+  switch (bn) {
+    case 32: return f32 ? gemm::gemm_tn_kernel<32, float> : gemm::gemm_tn_kernel<32, __nv_bfloat16>;
+    case 64: return f32 ? gemm::gemm_tn_kernel<64, float> : gemm::gemm_tn_kernel<64, __nv_bfloat16>;
+    case 128: return f32 ? gemm::gemm_tn_kernel<128, float> : gemm::gemm_tn_kernel<128, __nv_bfloat16>;
+    case 256: return f32 ? gemm::gemm_tn_kernel<256, float> : gemm::gemm_tn_kernel<256, __nv_bfloat16>;
+    default: return nullptr;
+  }
+}
+
+int elt_bytes(int dtype) {
+  switch (dtype) {
+    case B200_F16:
+    case B200_BF16: return 2;
+    case B200_E4M3: return 1;
+    case B200_F32: return 4;
+    default: return 0;
+  }
+}
+
+constexpr int kMaxSmemOptin = 232448;  // 227 KB: the sm_100 per-block opt-in limit
+constexpr int kDefaultSms = 148;
+
+// Packs B into the shared-memory image of each (n block, k block) tile: BN rows of 128 bytes,
+// 16-byte chunk c of row r stored at chunk position c ^ (r % 8) (the 128-byte swizzle), tiles
+// laid out n-block-major.  Rows >= N and K positions >= K are zero.  One thread per 16-byte chunk.
+// `preshuffled`: the input is shuffle_weight(B) (kittens_helpers.py:90-119), whose flat index
+// for logical (n, k) is ((((n/16 * K/32 + k/32) * 4 + (k%16)/4) * 16 + n%16) * 2 + (k%32)/16) * 4 + k%4.
+__global__ void __launch_bounds__(256) pack_b_kernel(const uint8_t* __restrict__ b_in, uint8_t* __restrict__ b_out,
+                                                     long long N, long long K, int eb, int bn, long long n_blocks,
+                                                     long long k_blocks, int preshuffled) {
+  const long long chunks_per_tile = static_cast<long long>(bn) * 8;
+  const long long total = n_blocks * k_blocks * chunks_per_tile;
+  const int elems_per_chunk = 16 / eb;
+  const int kb_elems = gemm::kRowBytes / eb;
+  for (long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < total;
+       g += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long tile = g / chunks_per_tile;
+    const int in_tile = static_cast<int>(g - tile * chunks_per_tile);
+    const int r = in_tile >> 3;
+    const int c = in_tile & 7;
+    const long long nb = tile / k_blocks;
+    const long long kb = tile - nb * k_blocks;
+    const long long n = nb * bn + r;
+    const long long k0 = kb * kb_elems + static_cast<long long>(c) * elems_per_chunk;
+    alignas(16) uint8_t chunk[16];
+    for (int e = 0; e < elems_per_chunk; ++e) {
+      const long long k = k0 + e;
+      for (int byte = 0; byte < eb; ++byte) {
+        uint8_t val = 0;
+        if (n < N && k < K) {
+          long long src;
+          if (preshuffled) {
+            const long long kbl = K / 32;
+            const long long kl = k % 32;
+            src = ((((n / 16 * kbl + k / 32) * 4 + (kl % 16) / 4) * 16 + n % 16) * 2 + kl / 16) * 4 + kl % 4;
+          } else {
+            src = n * K + k;
+          }
+          val = b_in[src * eb + byte];
+        }
+        chunk[e * eb + byte] = val;
+      }
+    }
+    uint8_t* dst = b_out + tile * (chunks_per_tile * 16) + static_cast<long long>(r) * 128 + ((c ^ (r & 7)) << 4);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(chunk);
+  }
+}
+
+// Streams a buffer larger than the L2 so that the next kernel starts from a cold cache.
+struct FlushState {
+  void* buf = nullptr;
+  size_t bytes = 0;
+  int device = -1;
+};
+FlushState g_flush;
+std::mutex g_flush_mu;
+
+}  // namespace
+
+struct b200_gemm_plan {
+  b200_gemm_desc desc;
+  int bn = 0;
+  int stages = 0;
+  int split_k = 1;
+  int grid = 0;
+  int sm_count = kDefaultSms;
+  int smem = 0;
+  int eb_ab = 2;
+  int kb_elems = 64;
+  int total_kb = 0;   // K blocks over the whole K (padded to a multiple of split_k)
+  int num_kb = 0;     // per split
+  int m_blocks = 0, n_blocks = 0;
+  int raster_group = 8;
+  KernelFn kernel = nullptr;
+  bool attr_set = false;
+  int attr_device = -1;
+  uint32_t* status = nullptr;  // device, 4 words, allocated on first run
+  int status_device = -1;
+  // Tensor maps are a pure function of (pointer, shape); cache the last pair.
+  const void* map_a_ptr = nullptr;
+  const void* map_b_ptr = nullptr;
+  CUtensorMap map_a, map_b;
+};
+
+namespace {
+
+bool direct_b(const b200_gemm_plan* p) { return p->desc.b_layout != B200_B_ROW_MAJOR_NK; }
+
+int64_t packed_b_bytes(const b200_gemm_plan* p) {
+  if (!direct_b(p)) return 0;
+  return static_cast<int64_t>(p->n_blocks) * p->total_kb * p->bn * gemm::kRowBytes;
+}
+
+int64_t workspace_bytes(const b200_gemm_plan* p) {
+  if (p->split_k <= 1) return 0;
+  return static_cast<int64_t>(p->split_k) * p->desc.M * p->desc.N * 4;
+}
+
+int ensure_device_state(b200_gemm_plan* plan) {
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  if (!plan->attr_set || plan->attr_device != dev) {
+    int cc_major = 0;
+    B200_CUDA_OK(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (cc_major != 10) {
+      return b200::fail(B200_ERR_NO_DEVICE, "device %d has compute capability %d.x; the GEMM kernels need sm_100", dev, cc_major);
+    }
+    B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(plan->kernel),
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
+    int sms = kDefaultSms;
+    B200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    plan->sm_count = sms;
+    const int items = plan->m_blocks * plan->n_blocks * plan->split_k;
+    int cap = plan->desc.max_ctas > 0 ? plan->desc.max_ctas : sms;
+    plan->grid = items < cap ? items : cap;
+    plan->attr_set = true;
+    plan->attr_device = dev;
+    plan->map_a_ptr = plan->map_b_ptr = nullptr;
+  }
+  if (plan->status == nullptr || plan->status_device != dev) {
+    if (plan->status != nullptr) cudaFree(plan->status);
+    plan->status = nullptr;
+    B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&plan->status), 4 * sizeof(uint32_t)));
+    B200_CUDA_OK(cudaMemset(plan->status, 0, 4 * sizeof(uint32_t)));
+    plan->status_device = dev;
+  }
+  return B200_OK;
+}
+
+int check_run_args(const b200_gemm_plan* plan, const void* A, const void* B, const void* C, const float* bias,
+                   const void* workspace, size_t workspace_bytes_in) {
+  B200_REQUIRE(plan != nullptr, "plan is NULL");
+  B200_REQUIRE(A && B && C, "gemm_run: A, B and C must be non-NULL");
+  B200_REQUIRE(((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u) == 0,
+               "gemm_run: A, B and C must be 16-byte aligned");
+  const bool needs_bias = plan->desc.epilogue == B200_EPI_BIAS_RELU || plan->desc.epilogue == B200_EPI_BIAS;
+  B200_REQUIRE(!needs_bias || bias != nullptr, "gemm_run: this plan's epilogue needs a bias vector");
+  const int64_t need = workspace_bytes(plan);
+  if (need > 0 && (workspace == nullptr || static_cast<int64_t>(workspace_bytes_in) < need)) {
+    return b200::fail(B200_ERR_WORKSPACE, "gemm_run: split-K needs a %lld-byte workspace, got %zu", (long long)need,
+                      workspace_bytes_in);
+  }
+  return B200_OK;
+}
+
+int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias, const float* scale_a,
+           const float* scale_b, void* workspace, cudaStream_t stream) {
+  const b200_gemm_desc& d = plan->desc;
+  if (plan->map_a_ptr != A) {
+    int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);
+    if (rc != B200_OK) return rc;
+    plan->map_a_ptr = A;
+  }
+  if (plan->map_b_ptr != B) {
+    if (direct_b(plan)) {
+      plan->map_b = plan->map_a;  // never dereferenced: packed B is streamed with 1-D bulk copies
+    } else {
+      int rc = make_operand_map(&plan->map_b, B, d.dtype_ab, static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.K),
+                                static_cast<uint32_t>(plan->bn));
+      if (rc != B200_OK) return rc;
+    }
+    plan->map_b_ptr = B;
+  }
+  Params p;
+  std::memset(&p, 0, sizeof(p));
+  p.M = static_cast<int>(d.M);
+  p.N = static_cast<int>(d.N);
+  p.K = static_cast<int>(d.K);
+  p.m_blocks = plan->m_blocks;
+  p.n_blocks = plan->n_blocks;
+  p.num_tiles = plan->m_blocks * plan->n_blocks;
+  p.num_kb = plan->num_kb;
+  p.kb_elems = plan->kb_elems;
+  p.split_k = plan->split_k;
+  p.stages = plan->stages;
+  p.raster_group = plan->raster_group;
+  p.kind_f8 = d.dtype_ab == B200_E4M3 ? 1 : 0;
+  p.idesc = sm100::make_idesc(d.dtype_ab == B200_BF16 ? 1u : 0u, gemm::kBM, static_cast<uint32_t>(plan->bn));
+  p.relu = (d.epilogue == B200_EPI_BIAS_RELU || d.epilogue == B200_EPI_RELU) ? 1 : 0;
+  p.bias_axis = d.bias_axis;
+  p.bias = (d.epilogue == B200_EPI_BIAS_RELU || d.epilogue == B200_EPI_BIAS) ? bias : nullptr;
+  p.scale_a = scale_a;
+  p.scale_b = scale_b;
+  p.C = C;
+  p.b_packed = direct_b(plan) ? B : nullptr;
+  p.workspace = static_cast<float*>(workspace);
+  p.status = plan->status;
+  plan->kernel<<<plan->grid, gemm::kThreads, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+  b200::count_launch();
+  B200_CUDA_OK(cudaGetLastError());
+  if (plan->split_k > 1) {
+    const size_t vecs = static_cast<size_t>(d.M) * d.N / 4 + 1;
+    size_t blocks = (vecs + 255) / 256;
+    const size_t cap = static_cast<size_t>(plan->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    if (d.dtype_c == B200_F32) {
+      gemm::splitk_reduce_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(p);
+    } else {
+      gemm::splitk_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(p);
+    }
+    b200::count_launch();
+    B200_CUDA_OK(cudaGetLastError());
+  }
+  return B200_OK;
+}
+
+int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace
+
+extern "C" {
+
+int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
+  B200_REQUIRE(desc != nullptr && out != nullptr, "gemm_plan_create: NULL argument");
+  *out = nullptr;
+  const b200_gemm_desc& d = *desc;
+  B200_REQUIRE(d.M >= 1 && d.N >= 1 && d.K >= 1, "gemm_plan_create: M, N, K must be >= 1 (got %lld, %lld, %lld)",
+               (long long)d.M, (long long)d.N, (long long)d.K);
+  B200_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256 && d.K < (1ll << 31) - 256,
+               "gemm_plan_create: each of M, N, K must be below 2^31");
+  B200_REQUIRE(d.dtype_ab == B200_F16 || d.dtype_ab == B200_BF16 || d.dtype_ab == B200_E4M3,
+               "gemm_plan_create: dtype_ab=%d is not f16, bf16 or e4m3", d.dtype_ab);
+  B200_REQUIRE(d.dtype_c == B200_F32 || d.dtype_c == B200_BF16, "gemm_plan_create: dtype_c=%d is not f32 or bf16", d.dtype_c);
+  B200_REQUIRE(d.b_layout >= B200_B_ROW_MAJOR_NK && d.b_layout <= B200_B_PACKED, "gemm_plan_create: bad b_layout %d", d.b_layout);
+  B200_REQUIRE(d.epilogue >= B200_EPI_NONE && d.epilogue <= B200_EPI_RELU, "gemm_plan_create: bad epilogue %d", d.epilogue);
+  B200_REQUIRE(d.bias_axis == B200_BIAS_AXIS_N || d.bias_axis == B200_BIAS_AXIS_M, "gemm_plan_create: bad bias_axis %d", d.bias_axis);
+  const int eb = elt_bytes(d.dtype_ab);
+  // TMA needs 16-byte multiples for the row pitch of A and B.
+  B200_REQUIRE((d.K * eb) % 16 == 0, "gemm_plan_create: K=%lld gives a %lld-byte row pitch; it must be a multiple of 16 bytes",
+               (long long)d.K, (long long)(d.K * eb));
+  if (d.b_layout == B200_B_REF_PRESHUFFLED) {
+    // Preconditions of the reference's shuffle_weight (kittens_helpers.py:107-108).
+    B200_REQUIRE(d.N % 16 == 0 && d.K % 32 == 0, "gemm_plan_create: preshuffled B needs N %% 16 == 0 and K %% 32 == 0");
+  }
+  B200_REQUIRE(d.tile_m == 0 || d.tile_m == gemm::kBM, "gemm_plan_create: tile_m=%d unsupported (128)", d.tile_m);
+  B200_REQUIRE(d.tile_n == 0 || d.tile_n == 32 || d.tile_n == 64 || d.tile_n == 128 || d.tile_n == 256,
+               "gemm_plan_create: tile_n=%d unsupported (32, 64, 128, 256)", d.tile_n);
+  const int kb_elems = gemm::kRowBytes / eb;
+  B200_REQUIRE(d.tile_k == 0 || d.tile_k == kb_elems, "gemm_plan_create: tile_k=%d unsupported (%d for this dtype)", d.tile_k, kb_elems);
+  B200_REQUIRE(d.cta_group == 0 || d.cta_group == 1, "gemm_plan_create: cta_group=%d unsupported (1)", d.cta_group);
+  B200_REQUIRE(d.stages >= 0 && d.stages <= gemm::kMaxStages, "gemm_plan_create: stages=%d outside [0,%d]", d.stages, gemm::kMaxStages);
+  B200_REQUIRE(d.split_k >= -1 && d.split_k <= 64, "gemm_plan_create: split_k=%d outside [-1,64]", d.split_k);
+  B200_REQUIRE(d.max_ctas >= 0 && d.raster_group >= 0, "gemm_plan_create: max_ctas and raster_group must be >= 0");
+
+  b200_gemm_plan* plan = new (std::nothrow) b200_gemm_plan();
+  if (plan == nullptr) return b200::fail(B200_ERR_INVALID, "gemm_plan_create: out of host memory");
+  plan->desc = d;
+  plan->desc.label[sizeof(plan->desc.label) - 1] = 0;
+  plan->eb_ab = eb;
+  plan->kb_elems = kb_elems;
+  plan->m_blocks = ceil_div(d.M, gemm::kBM);
+  const int k_blocks = ceil_div(d.K, kb_elems);
+
+  // Tile width: the widest tile whose tile count still fills the machine; wide tiles halve the
+  // shared-memory traffic per flop, narrow ones keep more SMs busy on small problems.
+  int bn = d.tile_n;
+  if (bn == 0) {
+    bn = 256;
+    while (bn > 64 && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, bn) < kDefaultSms) bn /= 2;
+    while (bn > 32 && bn / 2 >= d.N) bn /= 2;
+  }
+  plan->bn = bn;
+  plan->n_blocks = ceil_div(d.N, bn);
+
+  int split = d.split_k <= 1 ? 1 : d.split_k;
+  if (d.split_k == -1) {
+    // Skinny problems: too few tiles to occupy the SMs, so cut K until they do, keeping at
+    // least four K blocks per partition.
+    const int64_t tiles = static_cast<int64_t>(plan->m_blocks) * plan->n_blocks;
+    while (tiles * split * 2 <= kDefaultSms && k_blocks / (split * 2) >= 4 && split < 64) split *= 2;
+  }
+  if (split > k_blocks) split = k_blocks;
+  plan->split_k = split;
+  plan->num_kb = ceil_div(k_blocks, split);
+  plan->total_kb = plan->num_kb * split;
+
+  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024) / gemm::stage_bytes(bn);
+  int stages = d.stages > 0 ? d.stages : (max_stages < gemm::kMaxStages ? max_stages : gemm::kMaxStages);
+  if (stages > max_stages) {
+    delete plan;
+    return b200::fail(B200_ERR_INVALID, "gemm_plan_create: %d stages of %d bytes exceed the %d-byte shared memory limit", stages,
+                      gemm::stage_bytes(bn), kMaxSmemOptin);
+  }
+  plan->stages = stages;
+  plan->smem = gemm::smem_bytes(bn, stages);
+  // Two resident CTAs would both ask for TMEM; keep the footprint above half the SM's shared
+  // memory whenever two allocations (2 * tmem_columns) would not fit in the 512 columns.
+  if (2 * gemm::tmem_columns(bn) > 512 && plan->smem <= kMaxSmemOptin / 2) plan->smem = kMaxSmemOptin / 2 + 1024;
+  plan->raster_group = d.raster_group > 0 ? d.raster_group : 8;
+  plan->kernel = select_kernel(bn, d.dtype_c);
+  const int items = plan->m_blocks * plan->n_blocks * plan->split_k;
+  const int cap = d.max_ctas > 0 ? d.max_ctas : kDefaultSms;
+  plan->grid = items < cap ? items : cap;
+  *out = plan;
+  return B200_OK;
+}
+
+int b200_gemm_plan_destroy(b200_gemm_plan* plan) {
+  if (plan == nullptr) return B200_OK;
+  if (plan->status != nullptr) cudaFree(plan->status);
+  cudaGetLastError();
+  delete plan;
+  return B200_OK;
+}
+
+int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* out) {
+  B200_REQUIRE(plan != nullptr && out != nullptr, "gemm_plan_resources: NULL argument");
+  std::memset(out, 0, sizeof(*out));
+  out->tile_m = gemm::kBM;
+  out->tile_n = plan->bn;
+  out->tile_k = plan->kb_elems;
+  out->stages = plan->stages;
+  out->cta_group = 1;
+  out->split_k = plan->split_k;
+  out->grid_ctas = plan->grid;
+  out->block_threads = gemm::kThreads;
+  out->smem_bytes = plan->smem;
+  out->tmem_columns = gemm::tmem_columns(plan->bn);
+  out->ctas_per_sm = plan->smem > kMaxSmemOptin / 2 ? 1 : 2;
+  out->num_tiles = static_cast<int64_t>(plan->m_blocks) * plan->n_blocks;
+  out->workspace_bytes = workspace_bytes(plan);
+  out->packed_b_bytes = packed_b_bytes(plan);
+  // Registers per thread come from the loaded function; without a device this stays -1.
+  out->regs_per_thread = -1;
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, reinterpret_cast<const void*>(plan->kernel)) == cudaSuccess) {
+    out->regs_per_thread = fa.numRegs;
+  }
+  cudaGetLastError();
+  return B200_OK;
+}
+
+int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, void* stream) {
+  B200_REQUIRE(plan != nullptr && b_in != nullptr && b_packed != nullptr, "pack_b: NULL argument");
+  B200_REQUIRE(direct_b(plan), "pack_b: the plan's b_layout is row-major; nothing to pack");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(b_packed) & 15u) == 0, "pack_b: output must be 16-byte aligned");
+  const long long total = static_cast<long long>(plan->n_blocks) * plan->total_kb * plan->bn * 8;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  pack_b_kernel<<<static_cast<int>(blocks), 256, 0, b200::as_stream(stream)>>>(
+      static_cast<const uint8_t*>(b_in), static_cast<uint8_t*>(b_packed), plan->desc.N, plan->desc.K, plan->eb_ab, plan->bn,
+      plan->n_blocks, plan->total_kb, plan->desc.b_layout == B200_B_REF_PRESHUFFLED ? 1 : 0);
+  b200::count_launch();
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_gemm_run(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias, const float* scale_a,
+                  const float* scale_b, void* workspace, size_t workspace_bytes_in, void* stream) {
+  int rc = check_run_args(plan, A, B, C, bias, workspace, workspace_bytes_in);
+  if (rc != B200_OK) return rc;
+  rc = ensure_device_state(plan);
+  if (rc != B200_OK) return rc;
+  return launch(plan, A, B, C, bias, scale_a, scale_b, workspace, b200::as_stream(stream));
+}
+
+int b200_gemm_time(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias, const float* scale_a,
+                   const float* scale_b, void* workspace, size_t workspace_bytes_in, int iters, int flush_l2,
+                   float* times_ms) {
+  B200_REQUIRE(iters >= 1 && times_ms != nullptr, "gemm_time: iters must be >= 1 and times_ms non-NULL");
+  int rc = check_run_args(plan, A, B, C, bias, workspace, workspace_bytes_in);
+  if (rc != B200_OK) return rc;
+  rc = ensure_device_state(plan);
+  if (rc != B200_OK) return rc;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  B200_CUDA_OK(cudaEventCreate(&e0));
+  B200_CUDA_OK(cudaEventCreate(&e1));
+  for (int it = 0; it < iters && rc == B200_OK; ++it) {
+    if (flush_l2) rc = b200_flush_l2(nullptr);
+    if (rc != B200_OK) break;
+    cudaEventRecord(e0, nullptr);
+    rc = launch(plan, A, B, C, bias, scale_a, scale_b, workspace, nullptr);
+    cudaEventRecord(e1, nullptr);
+    cudaError_t e = cudaEventSynchronize(e1);
+    if (rc == B200_OK && e != cudaSuccess) rc = b200::fail(B200_ERR_CUDA, "gemm_time: %s", cudaGetErrorString(e));
+    if (rc == B200_OK) cudaEventElapsedTime(&times_ms[it], e0, e1);
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return rc;
+}
+
+int b200_gemm_time_batch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias,
+                         const float* scale_a, const float* scale_b, void* workspace, size_t workspace_bytes_in, int iters,
+                         float* total_ms) {
+  B200_REQUIRE(iters >= 1 && total_ms != nullptr, "gemm_time_batch: iters must be >= 1 and total_ms non-NULL");
+  int rc = check_run_args(plan, A, B, C, bias, workspace, workspace_bytes_in);
+  if (rc != B200_OK) return rc;
+  rc = ensure_device_state(plan);
+  if (rc != B200_OK) return rc;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  B200_CUDA_OK(cudaEventCreate(&e0));
+  B200_CUDA_OK(cudaEventCreate(&e1));
+  cudaEventRecord(e0, nullptr);
+  for (int it = 0; it < iters && rc == B200_OK; ++it) rc = launch(plan, A, B, C, bias, scale_a, scale_b, workspace, nullptr);
+  cudaEventRecord(e1, nullptr);
+  cudaError_t e = cudaEventSynchronize(e1);
+  if (rc == B200_OK && e != cudaSuccess) rc = b200::fail(B200_ERR_CUDA, "gemm_time_batch: %s", cudaGetErrorString(e));
+  if (rc == B200_OK) cudaEventElapsedTime(total_ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return rc;
+}
+
+int b200_status_read(b200_gemm_plan* plan, uint32_t words[4]) {
+  B200_REQUIRE(plan != nullptr && words != nullptr, "status_read: NULL argument");
+  words[0] = words[1] = words[2] = words[3] = 0;
+  if (plan->status == nullptr) return B200_OK;  // never launched
+  B200_CUDA_OK(cudaDeviceSynchronize());
+  B200_CUDA_OK(cudaMemcpy(words, plan->status, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (words[0] != 0) {
+    B200_CUDA_OK(cudaMemset(plan->status, 0, 4 * sizeof(uint32_t)));
+    return b200::fail(B200_ERR_TIMEOUT, "device wait timed out: code 0x%x cta %u tile %u k-block %u", words[0], words[1], words[2],
+                      words[3]);
+  }
+  return B200_OK;
+}
+
+int b200_flush_l2(void* stream) {
+  std::lock_guard<std::mutex> lock(g_flush_mu);
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  if (g_flush.buf == nullptr || g_flush.device != dev) {
+    if (g_flush.buf != nullptr) cudaFree(g_flush.buf);
+    g_flush.buf = nullptr;
+    int l2 = 0;
+    B200_CUDA_OK(cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev));
+    g_flush.bytes = static_cast<size_t>(l2) * 2;
+    if (g_flush.bytes < (256u << 20)) g_flush.bytes = 256u << 20;
+    B200_CUDA_OK(cudaMalloc(&g_flush.buf, g_flush.bytes));
+    g_flush.device = dev;
+  }
+  B200_CUDA_OK(cudaMemsetAsync(g_flush.buf, 0, g_flush.bytes, b200::as_stream(stream)));
+  return B200_OK;
+}
+
+}  // extern "C"

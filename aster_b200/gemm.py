@@ -1,0 +1,239 @@
+"""GEMM operator: plan objects over the C ABI and the host-buffer entry point.
+
+``GemmPlan`` wraps ``b200_gemm_plan_*`` / ``b200_gemm_run``.  :func:`gemm` is the call a user
+of the reference makes through ``execute_multitile_hsaco(cfg, artifact, iters, A, B)``
+(contrib/kittens/test/test_102_gemm_python_multitile_lds_cdna3.py:417-436): host arrays in,
+host array out, with the uploads and the download inside.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _native as nat
+from .dtypes import STORAGE
+from .execution import GpuBuffer
+
+DTYPE_CODES = {"f16": nat.F16, "bf16": nat.BF16, "e4m3": nat.E4M3, "f32": nat.F32}
+B_LAYOUT_CODES = {"row_major": nat.B_ROW_MAJOR_NK, "ref_preshuffled": nat.B_REF_PRESHUFFLED, "packed": nat.B_PACKED}
+EPILOGUE_CODES = {"none": nat.EPI_NONE, "bias_relu": nat.EPI_BIAS_RELU, "bias": nat.EPI_BIAS, "relu": nat.EPI_RELU}
+BIAS_AXIS_CODES = {"n": nat.BIAS_AXIS_N, "m": nat.BIAS_AXIS_M}
+
+
+def _ptr(x) -> Optional[C.c_void_p]:
+    if x is None:
+        return None
+    if isinstance(x, GpuBuffer):
+        return x.ptr
+    if isinstance(x, C.c_void_p):
+        return x
+    return C.c_void_p(int(x))
+
+
+class GemmPlan:
+    """A validated problem description bound to a kernel instance.
+
+    Parameters mirror ``b200_gemm_desc``.  ``tile_n``, ``stages``, ``split_k`` = 0 let the
+    library choose (``split_k=-1``: choose a K split for skinny problems).
+    """
+
+    def __init__(
+        self,
+        M: int,
+        N: int,
+        K: int,
+        dtype_ab: str = "f16",
+        dtype_c: str = "f32",
+        *,
+        b_layout: str = "row_major",
+        epilogue: str = "none",
+        bias_axis: str = "n",
+        tile_m: int = 0,
+        tile_n: int = 0,
+        tile_k: int = 0,
+        stages: int = 0,
+        cta_group: int = 0,
+        split_k: int = 0,
+        max_ctas: int = 0,
+        raster_group: int = 0,
+        label: str = "",
+    ) -> None:
+        self._handle = None
+        desc = nat.GemmDesc()
+        desc.M, desc.N, desc.K = int(M), int(N), int(K)
+        try:
+            desc.dtype_ab = DTYPE_CODES[dtype_ab]
+            desc.dtype_c = DTYPE_CODES[dtype_c]
+            desc.b_layout = B_LAYOUT_CODES[b_layout]
+            desc.epilogue = EPILOGUE_CODES[epilogue]
+            desc.bias_axis = BIAS_AXIS_CODES[bias_axis]
+        except KeyError as e:
+            raise ValueError(f"unknown enum value {e.args[0]!r}") from None
+        desc.tile_m, desc.tile_n, desc.tile_k = tile_m, tile_n, tile_k
+        desc.stages, desc.cta_group, desc.split_k = stages, cta_group, split_k
+        desc.max_ctas, desc.raster_group = max_ctas, raster_group
+        desc.label = label.encode()[:255]
+        handle = C.c_void_p()
+        nat.call("b200_gemm_plan_create", C.byref(desc), C.byref(handle))
+        self._handle = handle.value
+        self.M, self.N, self.K = int(M), int(N), int(K)
+        self.dtype_ab, self.dtype_c = dtype_ab, dtype_c
+        self.b_layout, self.epilogue, self.bias_axis = b_layout, epilogue, bias_axis
+        self.label = label
+
+    def __del__(self) -> None:
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+    def destroy(self) -> None:
+        if getattr(self, "_handle", None):
+            h, self._handle = self._handle, None
+            nat.call("b200_gemm_plan_destroy", C.c_void_p(h))
+
+    @property
+    def handle(self) -> C.c_void_p:
+        if not self._handle:
+            raise RuntimeError("plan was destroyed")
+        return C.c_void_p(self._handle)
+
+    @property
+    def total_flops(self) -> int:
+        return 2 * self.M * self.N * self.K
+
+    def resources(self) -> nat.GemmResources:
+        r = nat.GemmResources()
+        nat.call("b200_gemm_plan_resources", self.handle, C.byref(r))
+        return r
+
+    @property
+    def direct_b(self) -> bool:
+        return self.b_layout != "row_major"
+
+    def pack_b(self, b_in, b_packed, stream=None) -> None:
+        nat.call("b200_pack_b", self.handle, _ptr(b_in), _ptr(b_packed), _ptr(stream))
+
+    def run(self, A, B, Cbuf, bias=None, scale_a=None, scale_b=None, workspace=None, workspace_bytes=0, stream=None) -> None:
+        """Enqueue one launch.  All pointers are device addresses (GpuBuffer, int or c_void_p)."""
+        if isinstance(workspace, GpuBuffer) and not workspace_bytes:
+            workspace_bytes = workspace.size_bytes
+        nat.call(
+            "b200_gemm_run", self.handle, _ptr(A), _ptr(B), _ptr(Cbuf), _ptr(bias), _ptr(scale_a), _ptr(scale_b),
+            _ptr(workspace), workspace_bytes, _ptr(stream),
+        )
+
+    def time(self, A, B, Cbuf, bias=None, scale_a=None, scale_b=None, workspace=None, workspace_bytes=0,
+             iters: int = 100, flush_l2: bool = False) -> np.ndarray:
+        """Per-launch event-timed loop run natively; returns milliseconds per iteration."""
+        if isinstance(workspace, GpuBuffer) and not workspace_bytes:
+            workspace_bytes = workspace.size_bytes
+        out = (C.c_float * iters)()
+        nat.call(
+            "b200_gemm_time", self.handle, _ptr(A), _ptr(B), _ptr(Cbuf), _ptr(bias), _ptr(scale_a), _ptr(scale_b),
+            _ptr(workspace), workspace_bytes, iters, int(flush_l2), out,
+        )
+        return np.frombuffer(out, dtype=np.float32).copy()
+
+    def time_batch(self, A, B, Cbuf, bias=None, scale_a=None, scale_b=None, workspace=None, workspace_bytes=0,
+                   iters: int = 100) -> float:
+        """Milliseconds for ``iters`` back-to-back launches (one event pair)."""
+        if isinstance(workspace, GpuBuffer) and not workspace_bytes:
+            workspace_bytes = workspace.size_bytes
+        ms = C.c_float(0.0)
+        nat.call(
+            "b200_gemm_time_batch", self.handle, _ptr(A), _ptr(B), _ptr(Cbuf), _ptr(bias), _ptr(scale_a), _ptr(scale_b),
+            _ptr(workspace), workspace_bytes, iters, C.byref(ms),
+        )
+        return ms.value
+
+    def status(self) -> Sequence[int]:
+        """Device status words of the last launch; raises ``B200Error`` (TIMEOUT) if a wait gave up."""
+        words = (C.c_uint32 * 4)()
+        nat.call("b200_status_read", self.handle, words)
+        return list(words)
+
+
+def _check_operand(name: str, arr: np.ndarray, shape, dtype: str) -> np.ndarray:
+    want = STORAGE[dtype]
+    if not isinstance(arr, np.ndarray):
+        raise TypeError(f"{name}: expected numpy array, got {type(arr)}")
+    if arr.dtype != want:
+        raise TypeError(f"{name}: dtype {arr.dtype} does not store {dtype} (expected {np.dtype(want)})")
+    if int(np.prod(arr.shape)) != int(np.prod(shape)):
+        raise ValueError(f"{name}: {arr.shape} does not hold {tuple(shape)}")
+    return np.ascontiguousarray(arr)
+
+
+def gemm(
+    A: np.ndarray,
+    B: np.ndarray,
+    *,
+    dtype_ab: str = "f16",
+    dtype_c: str = "f32",
+    bias: Optional[np.ndarray] = None,
+    relu: bool = False,
+    bias_axis: str = "n",
+    scale_a: Optional[float] = None,
+    scale_b: Optional[float] = None,
+    shape: Optional[tuple] = None,
+    plan: Optional[GemmPlan] = None,
+    b_layout: str = "row_major",
+    **plan_kw,
+) -> np.ndarray:
+    """``C = epilogue(A . B^T)`` on the GPU with host arrays in and a host array out.
+
+    A is ``[M, K]``, B is ``[N, K]`` (both K-contiguous), stored as float16, or as bf16 /
+    e4m3 bit patterns (uint16 / uint8; see :mod:`aster_b200.dtypes`).  ``B`` in a direct-B
+    layout ("ref_preshuffled" or "packed" = row-major to be packed) is packed on the device
+    first.  Returns ``[M, N]`` float32, or bf16 bit patterns (uint16) for ``dtype_c="bf16"``.
+    """
+    if shape is None:
+        M, K = A.shape
+        N = B.shape[0]
+    else:
+        M, N, K = shape
+    A = _check_operand("A", A, (M, K), dtype_ab)
+    B = _check_operand("B", B, (N, K), dtype_ab)
+    if plan is None:
+        epilogue = {(False, False): "none", (True, True): "bias_relu", (True, False): "bias", (False, True): "relu"}[
+            (bias is not None, bool(relu))
+        ]
+        plan = GemmPlan(M, N, K, dtype_ab, dtype_c, b_layout=b_layout, epilogue=epilogue, bias_axis=bias_axis, **plan_kw)
+    res = plan.resources()
+    nat.call("b200_init", 0)
+    bufs = []
+
+    def dev(arr: np.ndarray) -> GpuBuffer:
+        b = GpuBuffer(arr.nbytes)
+        bufs.append(b)
+        b.copy_from_host(arr)
+        return b
+
+    try:
+        dA, dB = dev(A), dev(B)
+        if plan.direct_b:
+            packed = GpuBuffer(res.packed_b_bytes)
+            bufs.append(packed)
+            plan.pack_b(dB, packed)
+            dB = packed
+        dbias = dev(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
+        dsa = dev(np.array([scale_a], dtype=np.float32)) if scale_a is not None else None
+        dsb = dev(np.array([scale_b], dtype=np.float32)) if scale_b is not None else None
+        out = np.empty((M, N), dtype=STORAGE[dtype_c])
+        dC = GpuBuffer(out.nbytes)
+        bufs.append(dC)
+        ws = None
+        if res.workspace_bytes:
+            ws = GpuBuffer(res.workspace_bytes)
+            bufs.append(ws)
+        plan.run(dA, dB, dC, dbias, dsa, dsb, ws)
+        plan.status()
+        dC.copy_to_host(out)
+        return out
+    finally:
+        for b in bufs:
+            b.free()

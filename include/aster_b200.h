@@ -1,0 +1,202 @@
+/*
+ * aster_b200 C ABI: the drop-in boundary for ASTER's GEMM hot path on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, returns an int status
+ * (0 = B200_OK) and never throws.  The text of the most recent failure on the calling thread
+ * is available from b200_last_error().  Device pointers are raw CUDA device addresses; a
+ * `stream` argument is a cudaStream_t passed as void* (NULL = the legacy default stream, which
+ * is what the reference runtime launches on: python/aster/execution/core.py:562-597).
+ *
+ * Each group cites the reference interface it stands in for (paths are relative to the
+ * iree-org/aster source tree).
+ */
+#ifndef ASTER_B200_H_
+#define ASTER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------ */
+/* Status codes                                                                               */
+/* ------------------------------------------------------------------------------------------ */
+enum {
+  B200_OK = 0,
+  B200_ERR_INVALID = 1,     /* bad argument: shape, alignment, enum value, NULL pointer        */
+  B200_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed; see b200_last_error()         */
+  B200_ERR_UNSUPPORTED = 3, /* valid request that this build or device cannot serve            */
+  B200_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up; see b200_status_read()       */
+  B200_ERR_NO_DEVICE = 5,   /* no CUDA device / not an sm_100 part                              */
+  B200_ERR_WORKSPACE = 6    /* caller-provided workspace is missing or too small               */
+};
+
+/* Thread-local message of the last failing call ("" if none).  Mirrors the reference's
+ * "HIP error at file:line - msg" runtime_error text (python/lib/RuntimeModule.cpp:126-134). */
+const char* b200_last_error(void);
+const char* b200_version(void);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Runtime: stands in for the nanobind `hip_*` functions of python/lib/RuntimeModule.cpp       */
+/* ------------------------------------------------------------------------------------------ */
+
+typedef struct b200_props {
+  char name[128];
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t max_smem_per_block_optin; /* bytes */
+  int32_t smem_per_sm;              /* bytes */
+  int32_t regs_per_sm;
+  int32_t l2_bytes;
+  int32_t sm_clock_khz;
+  int32_t mem_clock_khz;
+  int32_t mem_bus_bits;
+  int64_t total_mem_bytes;
+} b200_props;
+
+int b200_init(int device);                        /* hip_init                RuntimeModule.cpp:143 */
+int b200_device_count(int* count);                /* hip_get_device_count    :336 */
+int b200_set_device(int device);                  /* hip_set_device          :343 */
+int b200_get_device(int* device);                 /* hip_get_device          :353 */
+int b200_device_props(int device, b200_props* p); /* hip_get_device_props    :169 */
+int b200_clear_last_error(void);                  /* hip_clear_last_error    :164 */
+int b200_device_synchronize(void);                /* hip_device_synchronize  :302 */
+/* hip_device_reset (:348) has no safe meaning on a shared GPU: always B200_ERR_UNSUPPORTED. */
+int b200_device_reset(void);
+
+int b200_malloc(void** dptr, size_t bytes);                         /* hip_malloc :307 */
+int b200_free(void* dptr);                                          /* hip_free   :314 */
+int b200_memcpy_h2d(void* dst, const void* src, size_t bytes);      /* hip_memcpy_host_to_device   :321 */
+int b200_memcpy_d2h(void* dst, const void* src, size_t bytes);      /* hip_memcpy_device_to_host   :326 */
+int b200_memcpy_d2d(void* dst, const void* src, size_t bytes);      /* hip_memcpy_device_to_device :331 */
+int b200_memset(void* dst, int value, size_t bytes);
+/* Pinned host memory, for end-to-end timing with host buffers. */
+int b200_host_alloc(void** hptr, size_t bytes);
+int b200_host_free(void* hptr);
+int b200_memcpy_h2d_async(void* dst, const void* src, size_t bytes, void* stream);
+int b200_memcpy_d2h_async(void* dst, const void* src, size_t bytes, void* stream);
+
+int b200_event_create(void** event);                                /* hip_event_create       :360 */
+int b200_event_destroy(void* event);                                /* hip_event_destroy      :367 */
+int b200_event_record(void* event, void* stream);                   /* hip_event_record       :376 */
+int b200_event_synchronize(void* event);                            /* hip_event_synchronize  :382 */
+int b200_event_elapsed_ms(void* start, void* stop, float* ms);      /* hip_event_elapsed_time :388 */
+int b200_stream_create(void** stream);                              /* hip_stream_create      :397 */
+int b200_stream_destroy(void* stream);                              /* hip_stream_destroy     :404 */
+int b200_stream_synchronize(void* stream);                          /* hip_stream_synchronize :413 */
+
+/* Evict the L2 by streaming a private buffer larger than the L2 (allocated on first use on the
+ * current device).  Stands in for FlushLLC (python/aster/execution/flush_llc.py:25-204). */
+int b200_flush_l2(void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* GEMM  C[M,N] = A[M,K] . B[N,K]^T, fp32 accumulation                                         */
+/* Stands in for compile_multitile_gemm + GpuModule (the "plan") and execute_multitile_hsaco   */
+/* (the "run"): contrib/kittens/test/test_102_gemm_python_multitile_lds_cdna3.py:391-436.      */
+/* ------------------------------------------------------------------------------------------ */
+
+enum { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3 };
+/* Layout of the B operand handed to b200_pack_b / b200_gemm_run. */
+enum {
+  B200_B_ROW_MAJOR_NK = 0,    /* B[N,K], K contiguous (reference OperandPath.LDS)                 */
+  B200_B_REF_PRESHUFFLED = 1, /* shuffle_weight(B): contrib/kittens/test/kittens_helpers.py:90-119 */
+  B200_B_PACKED = 2           /* row-major B that b200_pack_b turns into this plan's packed tiles  */
+};
+enum { B200_EPI_NONE = 0, B200_EPI_BIAS_RELU = 1, B200_EPI_BIAS = 2, B200_EPI_RELU = 3 };
+enum { B200_BIAS_AXIS_N = 0, B200_BIAS_AXIS_M = 1 };
+
+typedef struct b200_gemm_desc {
+  int64_t M, N, K;
+  int32_t dtype_ab;  /* B200_F16 | B200_BF16 | B200_E4M3                                        */
+  int32_t dtype_c;   /* B200_F32 | B200_BF16                                                    */
+  int32_t b_layout;  /* B200_B_*                                                                */
+  int32_t epilogue;  /* B200_EPI_*                                                              */
+  int32_t bias_axis; /* B200_BIAS_AXIS_*                                                        */
+  int32_t tile_m;    /* CTA tile rows: 128 (one CTA) or 256 (CTA pair); 0 = choose              */
+  int32_t tile_n;    /* CTA tile columns: 64, 128 or 256; 0 = choose                            */
+  int32_t tile_k;    /* elements per pipeline stage along K; 0 = 128 bytes' worth               */
+  int32_t stages;    /* shared-memory ring depth; 0 = as many as fit                            */
+  int32_t cta_group; /* 1 or 2 CTAs per MMA; 0 = choose                                         */
+  int32_t split_k;   /* K partitions reduced through an fp32 workspace; 0/1 = none, -1 = choose */
+  int32_t max_ctas;  /* persistent grid size cap; 0 = number of SMs                             */
+  int32_t raster_group; /* m-blocks per rasterisation group; 0 = choose                         */
+  int32_t reserved[3];
+  char label[256];   /* provenance only: the reference label string (gemm_config.py:678-701)    */
+} b200_gemm_desc;
+
+typedef struct b200_gemm_resources {
+  int32_t tile_m, tile_n, tile_k, stages, cta_group, split_k;
+  int32_t grid_ctas, block_threads;
+  int32_t smem_bytes;     /* dynamic shared memory per CTA                                      */
+  int32_t tmem_columns;   /* tensor-memory columns allocated per CTA                            */
+  int32_t regs_per_thread;
+  int32_t ctas_per_sm;
+  int64_t num_tiles;
+  int64_t workspace_bytes; /* required size of the run-time workspace (0 if none)               */
+  int64_t packed_b_bytes;  /* size of the packed B buffer (0 for row-major plans)               */
+} b200_gemm_resources;
+
+typedef struct b200_gemm_plan b200_gemm_plan;
+
+/* Validate the description (divisibility, alignment, enum values) and select a kernel
+ * instance.  Never undefined behaviour on bad input: returns B200_ERR_INVALID. */
+int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** plan);
+int b200_gemm_plan_destroy(b200_gemm_plan* plan);
+/* What the selected kernel needs; feeds the harness's post-compile resource filter
+ * (contrib/kittens/test/bench/bench_search.py:454-476). */
+int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* out);
+
+/* Convert B from the plan's declared caller layout (REF_PRESHUFFLED or PACKED = row-major
+ * input) into the packed tile image the direct-B kernel streams.  Runs once, outside the
+ * timed region, like the reference's host-side shuffle (bench_harness.py:567-574). */
+int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, void* stream);
+
+/* One launch.  A: [M,K] row-major.  B: [N,K] row-major, or the packed buffer for direct-B
+ * plans.  C: [M,N] row-major, fully overwritten.  bias: fp32, length N (or M), may be NULL
+ * when the epilogue has no bias.  scale_a / scale_b: device pointers to one fp32 each
+ * (per-tensor dequantisation scales), NULL = 1.0.  workspace: device scratch of at least
+ * resources.workspace_bytes (may be NULL when that is 0). */
+int b200_gemm_run(b200_gemm_plan* plan, const void* A, const void* B, void* C,
+                  const float* bias, const float* scale_a, const float* scale_b,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* The reference's timing loop done natively (python/aster/execution/core.py:698-703): for
+ * each of `iters` iterations [optional L2 flush] event, launch, event, synchronise.
+ * times_ms receives `iters` floats. */
+int b200_gemm_time(b200_gemm_plan* plan, const void* A, const void* B, void* C,
+                   const float* bias, const float* scale_a, const float* scale_b,
+                   void* workspace, size_t workspace_bytes, int iters, int flush_l2,
+                   float* times_ms);
+/* Same, but one event pair around `iters` back-to-back launches; *total_ms is their sum. */
+int b200_gemm_time_batch(b200_gemm_plan* plan, const void* A, const void* B, void* C,
+                         const float* bias, const float* scale_a, const float* scale_b,
+                         void* workspace, size_t workspace_bytes, int iters, float* total_ms);
+
+/* Device-side status words of the last launch of this plan (synchronises the device).
+ * words[0] = 0 when every bounded wait completed; otherwise a code naming the wait that gave
+ * up (role, barrier, tile).  Returns B200_ERR_TIMEOUT when words[0] != 0. */
+int b200_status_read(b200_gemm_plan* plan, uint32_t words[4]);
+/* Number of kernel launches issued by this library on the calling process so far. */
+int b200_launch_count(int64_t* count);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Bandwidth kernels                                                                          */
+/* ------------------------------------------------------------------------------------------ */
+
+/* c[i] = a[i] + b[i]; examples/03_vector_add/kernel.mlir:49-89 (int32, wrapping add). */
+int b200_vector_add_i32(const int32_t* a, const int32_t* b, int32_t* c, size_t n, void* stream);
+int b200_vector_add_f32(const float* a, const float* b, float* c, size_t n, void* stream);
+/* dst[M,N] = src[M,N], fp32 row-major, N % 4 == 0; elements outside MxN are not touched.
+ * `depth` (1..8) = 16-byte loads in flight per thread, `num_ctas` = persistent grid size
+ * (0 = a multiple of the SM count).  examples/06_copy_layout/copy_2d_padded.py:34-151. */
+int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, int depth,
+                            int num_ctas, void* stream);
+/* out[i] = max(a[i] + b[i], 0); examples/07_simple_fusion/simple_fusion.py:62-144. */
+int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASTER_B200_H_ */

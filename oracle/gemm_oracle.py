@@ -1,0 +1,275 @@
+"""CPU oracle for the GEMM hot path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in numpy, what the reference computes and checks for the path; the
+product (``aster_b200``) never imports it.  Only ``tests/``, ``__graft_entry__.smoke()`` and
+``bench.py``'s CPU-baseline / reference legs may use it, and only as the checker or as the
+timed CPU baseline.
+
+Parity status: PINNED.  The reference's own correctness oracle for every GEMM test and bench
+is numpy -- ``A.astype(np.float32) @ B.astype(np.float32).T`` -- so this restatement is the
+same arithmetic in the same library; it is additionally pinned by the reference's
+known-answer tests and by fixtures generated from the reference's pure-Python layer
+(``tests/golden/make_golden.py``).  Each function cites the reference lines it follows
+(paths relative to the iree-org/aster tree).
+
+Storage conventions: f16 = ``np.float16``; bf16 = ``np.uint16`` bit patterns; fp8-e4m3 (OCP
+e4m3fn) = ``np.uint8`` bit patterns.  Conversions here are written independently of the
+product's (``ml_dtypes`` when importable, bit arithmetic otherwise) so that tests can pit one
+against the other.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+try:  # present in the build image; the fallbacks below keep the oracle usable without it
+    import ml_dtypes as _mld
+except Exception:  # pragma: no cover
+    _mld = None
+
+E4M3_MAX = 448.0
+
+
+# ---------------------------------------------------------------------------------------------
+# element types
+# ---------------------------------------------------------------------------------------------
+def bf16_encode(x: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bits (uint16), round to nearest even."""
+    x = np.asarray(x, dtype=np.float32)
+    if _mld is not None:
+        return x.astype(_mld.bfloat16).view(np.uint16)
+    u = x.view(np.uint32).astype(np.uint64)
+    lsb = (u >> 16) & 1
+    return ((u + 0x7FFF + lsb) >> 16).astype(np.uint16)
+
+
+def bf16_decode(bits: np.ndarray) -> np.ndarray:
+    bits = np.asarray(bits, dtype=np.uint16)
+    if _mld is not None:
+        return bits.view(_mld.bfloat16).astype(np.float32)
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def e4m3_decode(bits: np.ndarray) -> np.ndarray:
+    bits = np.asarray(bits, dtype=np.uint8)
+    if _mld is not None:
+        return bits.view(_mld.float8_e4m3fn).astype(np.float32)
+    s = np.where(bits & 0x80, -1.0, 1.0)
+    e = ((bits >> 3) & 0xF).astype(np.int32)
+    m = (bits & 7).astype(np.float64)
+    v = np.where(e == 0, m * 2.0**-9, (1.0 + m / 8.0) * np.exp2(e - 7.0))
+    v = np.where((e == 15) & ((bits & 7) == 7), np.nan, v)
+    return (s * v).astype(np.float32)
+
+
+def e4m3_encode(x: np.ndarray) -> np.ndarray:
+    """float32 -> e4m3fn bits (uint8), round to nearest even; |x| is first clamped to 448."""
+    x = np.clip(np.asarray(x, dtype=np.float32), -E4M3_MAX, E4M3_MAX)
+    if _mld is not None:
+        return x.astype(_mld.float8_e4m3fn).view(np.uint8)
+    table = e4m3_decode(np.arange(256, dtype=np.uint8)).astype(np.float64)
+    pos = np.arange(0, 0x7F)  # non-negative finite codes, increasing in value
+    vals = table[pos]
+    a = np.abs(x).astype(np.float64)
+    hi = np.clip(np.searchsorted(vals, a, side="left"), 0, len(vals) - 1)
+    lo = np.clip(hi - 1, 0, len(vals) - 1)
+    d_lo, d_hi = np.abs(a - vals[lo]), np.abs(vals[hi] - a)
+    pick_hi = (d_hi < d_lo) | ((d_hi == d_lo) & (pos[hi] % 2 == 0))
+    code = np.where(pick_hi, pos[hi], pos[lo]).astype(np.uint8)
+    return code | np.where(np.signbit(x), 0x80, 0).astype(np.uint8)
+
+
+def decode(arr: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype == "f16":
+        return np.asarray(arr, dtype=np.float16).astype(np.float32)
+    if dtype == "bf16":
+        return bf16_decode(arr)
+    if dtype == "e4m3":
+        return e4m3_decode(arr)
+    if dtype == "f32":
+        return np.asarray(arr, dtype=np.float32)
+    raise ValueError(dtype)
+
+
+def encode(x: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype == "f16":
+        return np.asarray(x, dtype=np.float32).astype(np.float16)
+    if dtype == "bf16":
+        return bf16_encode(x)
+    if dtype == "e4m3":
+        return e4m3_encode(x)
+    if dtype == "f32":
+        return np.asarray(x, dtype=np.float32)
+    raise ValueError(dtype)
+
+
+def quantize_e4m3(x: np.ndarray):
+    """Per-tensor scale ``amax/448`` then e4m3 (the quantised-GEMM configuration).  Returns
+    (bits, scale:float32)."""
+    x = np.asarray(x, dtype=np.float32)
+    amax = np.float32(np.abs(x).max()) if x.size else np.float32(0)
+    scale = np.float32(amax / np.float32(E4M3_MAX)) if amax > 0 else np.float32(1)
+    return e4m3_encode(x / scale), scale
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------------
+def gemm_f32(A: np.ndarray, B: np.ndarray, dtype_ab: str = "f16") -> np.ndarray:
+    """``C[M,N] = A[M,K] . B[N,K]^T`` on float32-upcast inputs.
+
+    Exactly the reference's oracle: contrib/kittens/test/bench/bench_harness.py:821,1837;
+    contrib/kittens/test/test_102_gemm_python_multitile_lds_cdna3.py:504.
+    """
+    return decode(A, dtype_ab) @ decode(B, dtype_ab).T
+
+
+def gemm_epilogue(acc: np.ndarray, bias=None, relu: bool = False, bias_axis: str = "n", alpha: float = 1.0) -> np.ndarray:
+    """``max(acc * alpha + bias, 0)`` in float32: the add-then-max of the reference's fused
+    example (examples/07_simple_fusion/simple_fusion.py:140) applied to the accumulator."""
+    x = np.asarray(acc, dtype=np.float32)
+    if alpha != 1.0:
+        x = x * np.float32(alpha)
+    if bias is not None:
+        b = np.asarray(bias, dtype=np.float32)
+        x = x + (b[None, :] if bias_axis == "n" else b[:, None])
+    if relu:
+        x = np.maximum(x, np.float32(0))
+    return x.astype(np.float32)
+
+
+def gemm(A, B, dtype_ab="f16", dtype_c="f32", bias=None, relu=False, bias_axis="n", scale_a=None, scale_b=None):
+    """Full operator: GEMM, per-tensor scales, bias, ReLU, output cast (stored form)."""
+    alpha = 1.0
+    if scale_a is not None:
+        alpha = np.float32(alpha) * np.float32(scale_a)
+    if scale_b is not None:
+        alpha = np.float32(alpha) * np.float32(scale_b)
+    x = gemm_epilogue(gemm_f32(A, B, dtype_ab), bias, relu, bias_axis, float(alpha))
+    return encode(x, dtype_c)
+
+
+def gemm_scalar_f32(A: np.ndarray, B: np.ndarray, dtype_ab: str = "f16") -> np.ndarray:
+    """Plain-loop float32 accumulation in K order, for small cases (checks the BLAS call)."""
+    a, b = decode(A, dtype_ab), decode(B, dtype_ab)
+    M, K = a.shape
+    N = b.shape[0]
+    out = np.zeros((M, N), dtype=np.float32)
+    for k in range(K):
+        out += np.outer(a[:, k], b[:, k]).astype(np.float32)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# tolerances
+# ---------------------------------------------------------------------------------------------
+def abs_bound(A, B, dtype_ab: str) -> float:
+    """The stated fp16/bf16 bound: ``2e-3 * sqrt(K) * max|a| * max|b|``."""
+    a, b = decode(A, dtype_ab), decode(B, dtype_ab)
+    return 2e-3 * math.sqrt(a.shape[1]) * float(np.abs(a).max()) * float(np.abs(b).max())
+
+
+def rel_frobenius(got: np.ndarray, want: np.ndarray) -> float:
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    denom = np.linalg.norm(want)
+    return float(np.linalg.norm(got - want) / denom) if denom > 0 else float(np.linalg.norm(got))
+
+
+def bf16_ulp_distance(got_bits: np.ndarray, want_bits: np.ndarray) -> np.ndarray:
+    """Distance in bf16 code points between two bf16 arrays (sign-magnitude aware)."""
+
+    def ordered(b):
+        b = np.asarray(b, dtype=np.uint16).astype(np.int32)
+        return np.where(b & 0x8000, -(b & 0x7FFF), b & 0x7FFF)
+
+    return np.abs(ordered(got_bits) - ordered(want_bits))
+
+
+def assert_reference_close(got_f32, want_f32) -> None:
+    """The reference's own gate: ``assert_allclose(rtol=1e-2, atol=1e-2)``
+    (bench_harness.py:855; test_102_...lds_cdna3.py:505)."""
+    np.testing.assert_allclose(got_f32, want_f32, rtol=1e-2, atol=1e-2)
+
+
+# ---------------------------------------------------------------------------------------------
+# direct-B preshuffle
+# ---------------------------------------------------------------------------------------------
+def shuffle_weight(B: np.ndarray) -> np.ndarray:
+    """Host preshuffle of B[N,K] for the direct-B path.
+
+    Follows contrib/kittens/test/kittens_helpers.py:90-119: view B as
+    (n_block, n_lane=16, k_block, k_half=2, lane_group=4, k_within=4) and reorder to
+    (n_block, k_block, lane_group, n_lane, k_half, k_within); same shape and byte count.
+    """
+    N, K = B.shape
+    if N % 16 or K % 32:
+        raise AssertionError(f"N={N} must be a multiple of 16 and K={K} a multiple of 32")
+    v = B.reshape(N // 16, 16, K // 32, 2, 4, 4)
+    return np.ascontiguousarray(np.transpose(v, (0, 2, 4, 1, 3, 5))).reshape(N, K)
+
+
+def unshuffle_weight(S: np.ndarray) -> np.ndarray:
+    """Inverse of :func:`shuffle_weight`."""
+    N, K = S.shape
+    v = S.reshape(N // 16, K // 32, 4, 16, 2, 4)
+    return np.ascontiguousarray(np.transpose(v, (0, 3, 1, 4, 2, 5))).reshape(N, K)
+
+
+# ---------------------------------------------------------------------------------------------
+# bandwidth kernels
+# ---------------------------------------------------------------------------------------------
+def vector_add(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """examples/03_vector_add/run.py:44-53 (int32 add wraps like v_add_u32)."""
+    a, b = np.asarray(a), np.asarray(b)
+    if a.dtype == np.int32:
+        return (a.view(np.uint32) + b.view(np.uint32)).view(np.int32)
+    return (a.astype(np.float32) + b.astype(np.float32)).astype(np.float32)
+
+
+def copy_2d_padded(src: np.ndarray, dst: np.ndarray) -> np.ndarray:
+    """examples/06_copy_layout/copy_2d_padded.py:131-143: dst[:M,:N] = src, rest untouched."""
+    out = np.array(dst, copy=True)
+    m, n = src.shape
+    out[:m, :n] = src
+    return out
+
+
+def add_relu(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """examples/07_simple_fusion/simple_fusion.py:140: ``np.maximum(a + b, 0)`` in float32."""
+    return np.maximum(np.asarray(a, np.float32) + np.asarray(b, np.float32), np.float32(0))
+
+
+# ---------------------------------------------------------------------------------------------
+# seeded synthetic inputs
+# ---------------------------------------------------------------------------------------------
+def make_inputs(M: int, N: int, K: int, dtype_ab: str, dist: str, seed: int, with_bias: bool = False):
+    """Seeded operands: ``A <- default_rng(seed)``, ``B <- default_rng(seed+1)``,
+    ``bias <- default_rng(seed+2)`` (the reference seeds B with ``seed + 1``,
+    bench_harness.py:82-89).  ``dist``: "normal" = N(0,1), "uniform" = U(-1,1),
+    "normal0.1" = N(0, 0.1).  Values are drawn in float32 and cast to the storage type; for
+    e4m3 they are per-tensor quantised and the scales are returned.
+
+    Returns dict(A, B, bias, scale_a, scale_b).
+    """
+
+    def draw(rng, shape):
+        if dist == "uniform":
+            return rng.uniform(-1.0, 1.0, size=shape).astype(np.float32)
+        if dist == "normal0.1":
+            return (rng.standard_normal(size=shape) * 0.1).astype(np.float32)
+        return rng.standard_normal(size=shape).astype(np.float32)
+
+    a = draw(np.random.default_rng(seed), (M, K))
+    b = draw(np.random.default_rng(seed + 1), (N, K))
+    out = {"bias": None, "scale_a": None, "scale_b": None}
+    if dtype_ab == "e4m3":
+        out["A"], out["scale_a"] = quantize_e4m3(a)
+        out["B"], out["scale_b"] = quantize_e4m3(b)
+    else:
+        out["A"], out["B"] = encode(a, dtype_ab), encode(b, dtype_ab)
+    if with_bias:
+        out["bias"] = (np.random.default_rng(seed + 2).standard_normal(size=N) * 0.1).astype(np.float32)
+    return out
