@@ -115,6 +115,7 @@ SIGNATURES = {
     "b200_set_device": [C.c_int],
     "b200_get_device": [C.POINTER(C.c_int)],
     "b200_device_props": [C.c_int, C.POINTER(Props)],
+    "b200_device_pci_bus_id": [C.c_int, C.c_char_p, C.c_int],
     "b200_clear_last_error": [],
     "b200_device_synchronize": [],
     "b200_device_reset": [],
@@ -210,3 +211,9 @@ def device_props(device: int = 0) -> Props:
     p = Props()
     call("b200_device_props", device, C.byref(p))
     return p
+
+
+def device_pci_bus_id(device: int = 0) -> str:
+    buf = C.create_string_buffer(64)
+    call("b200_device_pci_bus_id", device, buf, 64)
+    return buf.value.decode()

@@ -97,6 +97,12 @@ int b200_device_props(int device, b200_props* p) {
   return B200_OK;
 }
 
+int b200_device_pci_bus_id(int device, char* buf, int len) {
+  B200_REQUIRE(buf != nullptr && len >= 16, "device_pci_bus_id: buffer of at least 16 bytes needed");
+  B200_CUDA_OK(cudaDeviceGetPCIBusId(buf, len, device));
+  return B200_OK;
+}
+
 int b200_clear_last_error(void) {
   // Clears the runtime's sticky-free error slot and this thread's message, like
   // hip_clear_last_error before each execute (python/aster/execution/core.py:656-662).

@@ -237,3 +237,127 @@ def gemm(
     finally:
         for b in bufs:
             b.free()
+
+
+class PinnedArray:
+    """A numpy array backed by page-locked host memory (``b200_host_alloc``)."""
+
+    def __init__(self, shape, dtype) -> None:
+        self._freed = True
+        self.nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        nat.call("b200_host_alloc", C.byref(p), self.nbytes)
+        self._ptr = p.value
+        self._freed = False
+        raw = (C.c_char * max(self.nbytes, 1)).from_address(self._ptr)
+        self.array = np.frombuffer(raw, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+
+    @property
+    def ptr(self) -> C.c_void_p:
+        return C.c_void_p(self._ptr)
+
+    def free(self) -> None:
+        if not getattr(self, "_freed", True):
+            self._freed = True
+            self.array = None
+            nat.call("b200_host_free", C.c_void_p(self._ptr))
+
+    def __del__(self) -> None:
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class HostGemmPipeline:
+    """Back-to-back GEMMs on host buffers with transfers overlapped with compute.
+
+    Each :meth:`submit` takes the host operands of one problem (pinned arrays from
+    :meth:`pinned_operands`) and enqueues upload -> GEMM -> download on one of ``depth``
+    streams, so the upload of problem i+1 and the download of problem i-1 overlap the GEMM of
+    problem i.  :meth:`result` waits for a slot and returns its pinned C array.  This is the
+    end-to-end path: every byte of A, B and C crosses PCIe for every problem.
+    """
+
+    def __init__(self, plan: GemmPlan, depth: int = 2, bias: Optional[np.ndarray] = None,
+                 scale_a: Optional[float] = None, scale_b: Optional[float] = None) -> None:
+        from .execution import GpuStream
+
+        if plan.direct_b:
+            raise ValueError("HostGemmPipeline takes row-major B")
+        self.plan = plan
+        self.depth = depth
+        res = plan.resources()
+        eb_ab = np.dtype(STORAGE[plan.dtype_ab]).itemsize
+        eb_c = np.dtype(STORAGE[plan.dtype_c]).itemsize
+        self.a_bytes, self.b_bytes = plan.M * plan.K * eb_ab, plan.N * plan.K * eb_ab
+        self.c_bytes = plan.M * plan.N * eb_c
+        nat.call("b200_init", _current_device())
+        self.streams = [GpuStream() for _ in range(depth)]
+        self.dA = [GpuBuffer(self.a_bytes) for _ in range(depth)]
+        self.dB = [GpuBuffer(self.b_bytes) for _ in range(depth)]
+        self.dC = [GpuBuffer(self.c_bytes) for _ in range(depth)]
+        self.ws = [GpuBuffer(res.workspace_bytes) if res.workspace_bytes else None for _ in range(depth)]
+        self.hC = [PinnedArray((plan.M, plan.N), STORAGE[plan.dtype_c]) for _ in range(depth)]
+        self._small = []
+        self.bias = self._upload_small(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
+        self.scale_a = self._upload_small(np.array([scale_a], np.float32)) if scale_a is not None else None
+        self.scale_b = self._upload_small(np.array([scale_b], np.float32)) if scale_b is not None else None
+        self._next = 0
+
+    def _upload_small(self, arr: np.ndarray) -> GpuBuffer:
+        buf = GpuBuffer(arr.nbytes)
+        buf.copy_from_host(arr)
+        self._small.append(buf)
+        return buf
+
+    def pinned_operands(self):
+        """Allocate pinned host arrays for one problem's A and B."""
+        return (PinnedArray((self.plan.M, self.plan.K), STORAGE[self.plan.dtype_ab]),
+                PinnedArray((self.plan.N, self.plan.K), STORAGE[self.plan.dtype_ab]))
+
+    @property
+    def h2d_bytes_per_problem(self) -> int:
+        return self.a_bytes + self.b_bytes
+
+    @property
+    def d2h_bytes_per_problem(self) -> int:
+        return self.c_bytes
+
+    def submit(self, hA: PinnedArray, hB: PinnedArray) -> int:
+        """Enqueue one problem; returns the slot to pass to :meth:`result`."""
+        slot = self._next
+        self._next = (self._next + 1) % self.depth
+        s = self.streams[slot]
+        s.synchronize()  # the slot's previous problem must have left its buffers
+        nat.call("b200_memcpy_h2d_async", self.dA[slot].ptr, hA.ptr, self.a_bytes, s.handle)
+        nat.call("b200_memcpy_h2d_async", self.dB[slot].ptr, hB.ptr, self.b_bytes, s.handle)
+        self.plan.run(self.dA[slot], self.dB[slot], self.dC[slot], self.bias, self.scale_a, self.scale_b,
+                      self.ws[slot], stream=s.handle)
+        nat.call("b200_memcpy_d2h_async", self.hC[slot].ptr, self.dC[slot].ptr, self.c_bytes, s.handle)
+        return slot
+
+    def result(self, slot: int) -> np.ndarray:
+        self.streams[slot].synchronize()
+        return self.hC[slot].array
+
+    def drain(self) -> None:
+        for s in self.streams:
+            s.synchronize()
+
+    def close(self) -> None:
+        self.drain()
+        for group in (self.dA, self.dB, self.dC, self.ws, self._small):
+            for buf in group:
+                if buf is not None:
+                    buf.free()
+        for h in self.hC:
+            h.free()
+        for s in self.streams:
+            s.destroy()
+
+
+def _current_device() -> int:
+    d = C.c_int(0)
+    nat.call("b200_get_device", C.byref(d))
+    return d.value

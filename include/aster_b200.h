@@ -61,6 +61,8 @@ int b200_device_count(int* count);                /* hip_get_device_count    :33
 int b200_set_device(int device);                  /* hip_set_device          :343 */
 int b200_get_device(int* device);                 /* hip_get_device          :353 */
 int b200_device_props(int device, b200_props* p); /* hip_get_device_props    :169 */
+/* PCI bus id ("0000:3b:00.0") of a device, to find the same GPU through NVML. */
+int b200_device_pci_bus_id(int device, char* buf, int len);
 int b200_clear_last_error(void);                  /* hip_clear_last_error    :164 */
 int b200_device_synchronize(void);                /* hip_device_synchronize  :302 */
 /* hip_device_reset (:348) has no safe meaning on a shared GPU: always B200_ERR_UNSUPPORTED. */

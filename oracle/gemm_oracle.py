@@ -188,6 +188,30 @@ def bf16_ulp_distance(got_bits: np.ndarray, want_bits: np.ndarray) -> np.ndarray
     return np.abs(ordered(got_bits) - ordered(want_bits))
 
 
+def bf16_ulp(x: np.ndarray) -> np.ndarray:
+    """Spacing of bf16 values at the magnitude of ``x`` (8 significand bits; the smallest
+    normal binade is used below it)."""
+    a = np.maximum(np.abs(np.asarray(x, dtype=np.float64)), 2.0**-126)
+    return np.exp2(np.floor(np.log2(a)) - 7)
+
+
+def bf16_output_error(got_bits: np.ndarray, want_f32: np.ndarray, accum_slack: float) -> float:
+    """Worst excess of ``|bf16 output - oracle f32|`` over the allowance of one bf16 spacing
+    at the oracle's magnitude plus ``accum_slack``, the absolute allowance for the different
+    fp32 summation orders of the GPU and of BLAS (which matters where terms cancel and the
+    result is far smaller than its addends).  <= 0 means within tolerance."""
+    got = bf16_decode(got_bits).astype(np.float64).reshape(np.shape(want_f32))
+    want = np.asarray(want_f32, dtype=np.float64)
+    return float(np.max(np.abs(got - want) - bf16_ulp(want) - accum_slack))
+
+
+def accumulation_slack(A, B, dtype_ab: str, alpha: float = 1.0) -> float:
+    """Absolute allowance for fp32 summation-order differences: ``1e-6 * K * max|a| * max|b|``
+    (about 16x the typical ``K * 2^-24`` drift of a length-K fp32 dot product)."""
+    a, b = decode(A, dtype_ab), decode(B, dtype_ab)
+    return 1e-6 * a.shape[1] * float(np.abs(a).max()) * float(np.abs(b).max()) * abs(alpha)
+
+
 def assert_reference_close(got_f32, want_f32) -> None:
     """The reference's own gate: ``assert_allclose(rtol=1e-2, atol=1e-2)``
     (bench_harness.py:855; test_102_...lds_cdna3.py:505)."""

@@ -1,0 +1,330 @@
+"""GEMM parity on a B200: the CUDA path (through the C ABI) against the CPU oracle on the same
+seeded inputs.  The matrix follows the reference's own test classes
+(contrib/kittens/test/test_102_gemm_python_multitile_lds_cdna3.py:515-702 and the direct-B
+twin): geometry, pipeline depth x K length, multi-workgroup, plus the element types, the
+fused epilogue, the scaled fp8 path, split-K and the configured full-size problems.
+
+Tolerances (stated once here, used below):
+* f16 / bf16 inputs, f32 output: max |err| <= 2e-3 * sqrt(K) * max|a| * max|b|, and the
+  reference's own gate rtol = atol = 1e-2 where the reference uses it.
+* bf16 output: |out - oracle f32| <= one bf16 spacing at the oracle's magnitude, plus
+  1e-6 * K * max|a| * max|b| for the different fp32 summation orders of GPU and BLAS.
+* e4m3: relative Frobenius error <= 2 % against the oracle built from the same quantised inputs.
+"""
+
+import math
+import tempfile
+
+import numpy as np
+import pytest
+
+from aster_b200.gemm import GemmPlan, gemm
+from aster_b200.gemm_config import B200GemmInstance, GemmMappingSpec, GemmSpec, OperandPath, make_b200_instance
+from aster_b200.kittens_helpers import PIPELINE_STRATEGIES
+from aster_b200.multitile_gemm import compile_multitile_gemm, execute_multitile_hsaco
+from oracle import gemm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def check(got, inp, dtype_ab, dtype_c, *, bias=None, relu=False, bias_axis="n"):
+    alpha = 1.0
+    if inp["scale_a"] is not None:
+        alpha = float(np.float32(inp["scale_a"]) * np.float32(inp["scale_b"]))
+    want = orc.gemm_epilogue(orc.gemm_f32(inp["A"], inp["B"], dtype_ab), bias, relu, bias_axis, alpha)
+    got_f32 = orc.decode(got, dtype_c).reshape(want.shape)
+    if dtype_ab == "e4m3":
+        want_c = orc.decode(orc.encode(want, dtype_c), dtype_c)
+        rel = orc.rel_frobenius(got_f32, want_c)
+        assert rel <= 0.02, f"relative Frobenius error {rel}"
+        # accumulation is exact enough that the error is far below the budget
+        assert rel <= 1e-3
+    elif dtype_c == "f32":
+        bound = orc.abs_bound(inp["A"], inp["B"], dtype_ab) * (abs(alpha) if alpha != 1.0 else 1.0)
+        err = float(np.max(np.abs(got_f32 - want)))
+        assert err <= bound, f"max |err| {err} > {bound}"
+    else:
+        excess = orc.bf16_output_error(got, want, orc.accumulation_slack(inp["A"], inp["B"], dtype_ab, alpha))
+        assert excess <= 0.0, f"bf16 output exceeds one bf16 spacing + accumulation slack by {excess}"
+
+
+def run(M, N, K, dtype_ab="f16", dtype_c="f32", dist="normal", seed=0, bias=False, relu=False, bias_axis="n", **kw):
+    inp = orc.make_inputs(M, N, K, dtype_ab, dist, seed, with_bias=False)
+    b = None
+    if bias:
+        b = (np.random.default_rng(seed + 2).standard_normal(N if bias_axis == "n" else M) * 0.1).astype(np.float32)
+    got = gemm(inp["A"], inp["B"], dtype_ab=dtype_ab, dtype_c=dtype_c, bias=b, relu=relu, bias_axis=bias_axis,
+               scale_a=inp["scale_a"], scale_b=inp["scale_b"], **kw)
+    check(got, inp, dtype_ab, dtype_c, bias=b, relu=relu, bias_axis=bias_axis)
+    return got
+
+
+class TestKnownAnswers:
+    """The reference's single-instruction known answers, through the full kernel."""
+
+    def test_f16_ones_times_twos(self, gpu):
+        a = np.ones((16, 16), np.float16)
+        b = np.full((16, 16), 2.0, np.float16)
+        assert np.all(gemm(a, b) == 32.0)
+
+    @pytest.mark.parametrize("dtype", ["f16", "bf16"])
+    def test_ones_k32(self, gpu, dtype):
+        ones = orc.encode(np.ones((16, 32), np.float32), dtype)
+        assert np.all(gemm(ones, ones, dtype_ab=dtype) == 32.0)
+
+    def test_fp8_ones_and_initial_accumulator(self, gpu):
+        ones = orc.encode(np.ones((16, 32), np.float32), "e4m3")
+        assert np.all(gemm(ones, ones, dtype_ab="e4m3") == 32.0)
+        a = orc.encode(np.full((16, 32), 1.5, np.float32), "e4m3")
+        b = orc.encode(np.full((16, 32), 2.0, np.float32), "e4m3")
+        assert np.all(gemm(a, b, dtype_ab="e4m3", bias=np.full(16, 10.0, np.float32)) == 106.0)
+
+    def test_scaled_fp8(self, gpu):
+        a = orc.encode(np.full((16, 128), 1.75, np.float32), "e4m3")
+        b = orc.encode(np.full((16, 128), 1.25, np.float32), "e4m3")
+        assert np.all(gemm(a, b, dtype_ab="e4m3", scale_a=4.0, scale_b=2.0) == 2240.0)
+
+    def test_bf16_tile_64(self, gpu):
+        a = orc.encode(np.ones((16, 32), np.float32), "bf16")
+        b = orc.encode(np.full((16, 32), 2.0, np.float32), "bf16")
+        assert np.all(gemm(a, b, dtype_ab="bf16") == 64.0)
+
+
+def reference_style_instance(num_workgroups, num_waves_per_wg, num_tiles_per_wg, k_mult, pipeline_strategy=1,
+                             operand_path=OperandPath.LDS, **mapping_kw):
+    """``_make_instance`` of the reference tests: sizes follow from the mapping."""
+    tiles_per_wave = [t // w for t, w in zip(num_tiles_per_wg, num_waves_per_wg)]
+    M = num_workgroups[0] * num_tiles_per_wg[0] * 16
+    N = num_workgroups[1] * num_tiles_per_wg[1] * 16
+    K = k_mult * num_tiles_per_wg[2] * 32
+    mapping = GemmMappingSpec(num_workgroups, num_waves_per_wg, tiles_per_wave, pipeline_strategy=pipeline_strategy,
+                              operand_path=operand_path, **mapping_kw)
+    return B200GemmInstance(GemmSpec.from_sizes(M, N, K), mapping)
+
+
+def run_reference_style(cfg):
+    """``_run_multitile`` of the reference tests: seed 42+M+N+K, randn * 0.1 in f16, compile to
+    a temporary artifact, execute once, numpy oracle with rtol = atol = 1e-2."""
+    M, N, K = cfg.gemm_size
+    np.random.seed(42 + M + N + K)
+    A = (np.random.randn(M, K) * 0.1).astype(np.float16)
+    B = (np.random.randn(N, K) * 0.1).astype(np.float16)
+    with tempfile.NamedTemporaryFile(suffix=".b200plan.json") as tmp:
+        compile_multitile_gemm(cfg, tmp.name)
+        C, times = execute_multitile_hsaco(cfg, tmp.name, 1, A, B)
+    assert len(times) == 1 and times[0] > 0
+    orc.assert_reference_close(C, orc.gemm_f32(A, B).reshape(-1))
+
+
+GEOMETRIES = [
+    ([1, 1, 1], [3, 2, 1]), ([1, 1, 1], [2, 2, 3]), ([2, 1, 1], [6, 2, 1]), ([2, 2, 1], [8, 4, 1]),
+    ([2, 2, 1], [6, 4, 1]), ([2, 2, 1], [6, 6, 1]), ([4, 1, 1], [8, 7, 1]), ([4, 1, 1], [12, 5, 1]),
+    ([1, 4, 1], [10, 8, 1]), ([4, 2, 1], [12, 6, 1]), ([2, 4, 1], [8, 8, 1]), ([2, 4, 1], [12, 8, 1]),
+]
+
+
+class TestGeometry:
+    """Wave-geometry sweep of the reference (test_102_..._lds_cdna3.py:515-562)."""
+
+    @pytest.mark.parametrize("waves,tiles", GEOMETRIES)
+    def test_correctness(self, gpu, waves, tiles):
+        run_reference_style(reference_style_instance([1, 1, 1], waves, tiles, k_mult=4, pipeline_strategy=3))
+
+
+class TestPipeline:
+    """Pipeline strategy x K length (test_102_..._lds_cdna3.py:565-595): the strategy's depth is
+    the shared-memory ring depth here, so short K against deep rings is the interesting corner."""
+
+    @pytest.mark.parametrize("waves,tiles", [([2, 2, 1], [6, 4, 1]), ([4, 2, 1], [12, 6, 1])])
+    @pytest.mark.parametrize("k_mult", [2, 4, 8])
+    @pytest.mark.parametrize("pipeline_strategy", [1, 2, 3, 4, 5, 6, 9])
+    def test_correctness(self, gpu, waves, tiles, k_mult, pipeline_strategy):
+        if k_mult < max(PIPELINE_STRATEGIES[pipeline_strategy].values()) + 1:
+            pytest.skip("fewer K iterations than pipeline stages (the reference skips these too)")
+        run_reference_style(reference_style_instance([1, 1, 1], waves, tiles, k_mult, pipeline_strategy))
+
+
+class TestMultiWG:
+    @pytest.mark.parametrize("wg", [[2, 2, 1], [3, 1, 1], [1, 5, 1], [4, 3, 1], [19, 2, 1]])
+    def test_correctness(self, gpu, wg):
+        run_reference_style(reference_style_instance(wg, [2, 2, 1], [8, 8, 1], k_mult=8, pipeline_strategy=3))
+
+    def test_label_knobs_do_not_change_results(self, gpu):
+        run_reference_style(reference_style_instance([2, 2, 1], [2, 2, 1], [8, 8, 1], 8, 5, ll_sched=1, hoist_wait=True,
+                                                     rotate_compute_stage=True, use_conservative_barriers=True))
+
+
+class TestDirectB:
+    """B handed over in the reference's preshuffled order (test_102_..._directb_cdna3.py)."""
+
+    @pytest.mark.parametrize("wg,waves,tiles,k_mult", [
+        ([1, 1, 1], [1, 1, 1], [3, 2, 1], 4), ([1, 1, 1], [2, 2, 1], [8, 4, 1], 4),
+        ([2, 3, 1], [1, 4, 1], [8, 16, 1], 8), ([2, 2, 1], [2, 2, 1], [6, 6, 2], 4),
+    ])
+    def test_correctness(self, gpu, wg, waves, tiles, k_mult):
+        run_reference_style(reference_style_instance(wg, waves, tiles, k_mult, 3, operand_path=OperandPath.DIRECT_B))
+
+    def test_packed_row_major_input(self, gpu):
+        run(384, 640, 512, b_layout="packed")
+        run(200, 136, 264, b_layout="packed", tile_n=64)
+
+    def test_direct_b_equals_staged_b_bitwise(self, gpu):
+        inp = orc.make_inputs(256, 512, 1024, "bf16", "uniform", 9)
+        staged = gemm(inp["A"], inp["B"], dtype_ab="bf16", tile_n=128)
+        direct = gemm(inp["A"], inp["B"], dtype_ab="bf16", tile_n=128, b_layout="packed")
+        assert np.array_equal(staged, direct)
+
+
+class TestShapesAndTypes:
+    @pytest.mark.parametrize("tile_n", [32, 64, 128, 256])
+    def test_tile_widths(self, gpu, tile_n):
+        run(256, 512, 384, tile_n=tile_n)
+
+    @pytest.mark.parametrize("shape", [(1, 8, 8), (16, 16, 16), (48, 32, 128), (130, 70, 72), (127, 255, 1000),
+                                       (129, 257, 1032), (300, 36, 200), (5, 1000, 64)])
+    @pytest.mark.parametrize("dtype_c", ["f32", "bf16"])
+    def test_ragged(self, gpu, shape, dtype_c):
+        run(*shape, "bf16", dtype_c, "uniform", seed=sum(shape))
+
+    @pytest.mark.parametrize("stages", [1, 2, 3, 5, 8])
+    def test_ring_depths(self, gpu, stages):
+        run(256, 256, 2048, "bf16", "f32", "uniform", 1, tile_n=64, stages=stages)
+
+    @pytest.mark.parametrize("max_ctas", [1, 7, 148])
+    def test_persistent_grid_sizes(self, gpu, max_ctas):
+        run(1024, 1536, 256, "bf16", "bf16", "uniform", 1, max_ctas=max_ctas, tile_n=128)
+
+    @pytest.mark.parametrize("raster_group", [1, 3, 8, 64])
+    def test_rasterisation(self, gpu, raster_group):
+        run(1280, 1024, 128, "f16", "f32", raster_group=raster_group, tile_n=128)
+
+    def test_empty_k_tail_and_zero_inputs(self, gpu):
+        a = np.zeros((128, 64), np.float16)
+        assert not gemm(a, a).any()
+
+
+class TestEpilogue:
+    @pytest.mark.parametrize("dtype_c", ["f32", "bf16"])
+    @pytest.mark.parametrize("bias,relu", [(True, True), (True, False), (False, True)])
+    def test_bias_relu(self, gpu, dtype_c, bias, relu):
+        run(384, 512, 256, "bf16", dtype_c, "normal", 2, bias=bias, relu=relu)
+
+    def test_bias_per_row(self, gpu):
+        run(384, 512, 256, "bf16", "bf16", "normal", 2, bias=True, relu=True, bias_axis="m")
+
+    def test_relu_actually_clamps(self, gpu):
+        got = run(256, 256, 256, "bf16", "f32", "normal", 2, bias=True, relu=True)
+        assert got.min() == 0.0 and (got == 0.0).mean() > 0.3
+
+    def test_ragged_with_bias(self, gpu):
+        run(130, 70, 72, "bf16", "bf16", "normal", 2, bias=True, relu=True)
+
+
+class TestFp8:
+    @pytest.mark.parametrize("shape", [(128, 128, 128), (512, 512, 512), (200, 136, 272), (256, 1024, 4096)])
+    @pytest.mark.parametrize("dtype_c", ["bf16", "f32"])
+    def test_scaled(self, gpu, shape, dtype_c):
+        run(*shape, "e4m3", dtype_c, "normal", 3)
+
+    def test_against_unquantised_inputs_is_quantisation_noise(self, gpu):
+        rng = np.random.default_rng(3)
+        a = rng.standard_normal((256, 1024)).astype(np.float32)
+        b = rng.standard_normal((256, 1024)).astype(np.float32)
+        (qa, sa), (qb, sb) = orc.quantize_e4m3(a), orc.quantize_e4m3(b)
+        got = gemm(qa, qb, dtype_ab="e4m3", dtype_c="f32", scale_a=float(sa), scale_b=float(sb))
+        assert 0.02 < orc.rel_frobenius(got, a @ b.T) < 0.06
+
+
+class TestSplitK:
+    @pytest.mark.parametrize("M", [16, 128])
+    @pytest.mark.parametrize("split_k", [2, 4, 8, -1])
+    def test_skinny(self, gpu, M, split_k):
+        run(M, 1024, 4096, "bf16", "bf16", "uniform", 4, split_k=split_k, tile_n=64)
+
+    def test_uneven_split_and_epilogue(self, gpu):
+        run(48, 200, 1000, "bf16", "f32", "uniform", 4, split_k=3, tile_n=64, bias=True, relu=True)
+        run(48, 203, 1000 + 8, "bf16", "f32", "uniform", 4, split_k=5, tile_n=32)
+
+    def test_split_k_is_deterministic(self, gpu):
+        inp = orc.make_inputs(16, 512, 8192, "bf16", "uniform", 4)
+        outs = [gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", split_k=8, tile_n=64) for _ in range(3)]
+        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+
+
+class TestConfiguredProblems:
+    """The configured workloads at full size (seeds as configured)."""
+
+    def test_fp16_512(self, gpu):
+        inp = orc.make_inputs(512, 512, 512, "f16", "normal", 0)
+        got = gemm(inp["A"], inp["B"])
+        check(got, inp, "f16", "f32")
+        orc.assert_reference_close(got, orc.gemm_f32(inp["A"], inp["B"]))
+
+    def test_bf16_4096(self, gpu):
+        inp = orc.make_inputs(4096, 4096, 4096, "bf16", "uniform", 1)
+        check(gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="f32"), inp, "bf16", "f32")
+        check(gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16"), inp, "bf16", "bf16")
+
+    def test_fused_epilogue_8192x8192x2048(self, gpu):
+        inp = orc.make_inputs(8192, 8192, 2048, "bf16", "normal", 2, with_bias=True)
+        got = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", bias=inp["bias"], relu=True)
+        check(got, inp, "bf16", "bf16", bias=inp["bias"], relu=True)
+
+    def test_fp8_8192_rows_sample(self, gpu):
+        # The full 8192^3 product on the GPU; the oracle checks a fixed random sample of 512 rows
+        # (each row of C depends on one row of A and all of B).
+        inp = orc.make_inputs(8192, 8192, 8192, "e4m3", "normal", 3)
+        got = gemm(inp["A"], inp["B"], dtype_ab="e4m3", dtype_c="bf16", scale_a=inp["scale_a"], scale_b=inp["scale_b"])
+        rows = np.sort(np.random.default_rng(0).choice(8192, 512, replace=False))
+        sub = dict(inp, A=inp["A"][rows])
+        check(got[rows], sub, "e4m3", "bf16")
+
+    @pytest.mark.parametrize("M", [16, 128])
+    def test_decode_shapes(self, gpu, M):
+        inp = orc.make_inputs(M, 8192, 8192, "bf16", "uniform", 4)
+        got = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", split_k=-1, tile_n=64)
+        check(got, inp, "bf16", "bf16")
+
+
+class TestProperties:
+    """Size-independent properties, usable where a full oracle pass would be slow."""
+
+    def test_linearity_in_a(self, gpu):
+        rng = np.random.default_rng(12)
+        a1 = rng.integers(-4, 5, (512, 1024)).astype(np.float16)
+        a2 = rng.integers(-4, 5, (512, 1024)).astype(np.float16)
+        b = rng.integers(-4, 5, (768, 1024)).astype(np.float16)
+        # small integers: every product and partial sum is exact in fp32, so linearity is exact
+        assert np.array_equal(gemm(a1 + a2, b), gemm(a1, b) + gemm(a2, b))
+
+    def test_row_shards_are_slices_of_the_whole(self, gpu):
+        inp = orc.make_inputs(1024, 512, 512, "bf16", "uniform", 4)
+        whole = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", tile_n=128)
+        for g in (2, 4, 8):
+            rows = 1024 // g
+            parts = [gemm(inp["A"][r * rows:(r + 1) * rows], inp["B"], dtype_ab="bf16", dtype_c="bf16", tile_n=128) for r in range(g)]
+            assert np.array_equal(np.concatenate(parts), whole)
+
+    def test_identity_b_returns_a(self, gpu):
+        a = orc.make_inputs(300, 256, 256, "bf16", "uniform", 8)["A"]
+        eye = orc.encode(np.eye(256, dtype=np.float32), "bf16")
+        assert np.array_equal(gemm(a, eye, dtype_ab="bf16", dtype_c="bf16"), a)
+
+
+class TestPlanObject:
+    def test_timing_loops_and_status(self, gpu):
+        from aster_b200.execution import GpuBuffer
+
+        plan = GemmPlan(1024, 1024, 1024, "bf16", "bf16")
+        bufs = [GpuBuffer(1024 * 1024 * 2) for _ in range(3)]
+        for b in bufs:
+            b.zero()
+        t = plan.time(*bufs, iters=5)
+        assert t.shape == (5,) and (t > 0).all()
+        tf = plan.time(*bufs, iters=3, flush_l2=True)
+        assert (tf > 0).all()
+        assert plan.time_batch(*bufs, iters=4) > 0
+        assert plan.status() == [0, 0, 0, 0]
+        assert plan.resources().regs_per_thread > 0
+        for b in bufs:
+            b.free()
