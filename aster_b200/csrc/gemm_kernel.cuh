@@ -45,6 +45,8 @@ constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
 constexpr unsigned long long kDrainTimeoutNs = 20000000ull;   // 20 ms
 
 // Status codes (status[0]); status[1] = blockIdx.x, status[2] = tile, status[3] = k block.
+// status[4..5] = SM cycles and status[6..7] = nanoseconds that CTA 0 spent in the kernel (the
+// SM clock actually seen by the launch is their ratio).
 enum : uint32_t {
   kStatusOk = 0,
   kStatusProducerEmptyWait = 0x10,
@@ -55,7 +57,7 @@ enum : uint32_t {
 
 struct Params {
   int M, N, K;
-  int m_blocks, n_blocks;
+  int m_blocks, n_blocks;  // tiles along M (128 rows, or 256 for a CTA pair) and N
   int num_tiles;       // m_blocks * n_blocks
   int num_kb;          // K blocks per tile (per split)
   int kb_elems;        // elements of K per stage (128 B / element size)
@@ -73,23 +75,32 @@ struct Params {
   const void* b_packed;  // non-null: B comes as packed tile images, streamed with 1-D bulk copies
   float* workspace;      // split-K partial sums [split][M][N] fp32
   uint32_t* status;
+  int debug_mode;  // 0 = normal; 1 = producer signals without copying; 2 = MMA warp commits without multiplying
 };
 
-__host__ __device__ constexpr int stage_bytes(int bn) { return (kBM + bn) * kRowBytes; }
+__host__ __device__ constexpr int stage_bytes(int bn, int cg = 1) { return (kBM + bn / cg) * kRowBytes; }
 // Barrier block that follows the stage ring: full[8], empty[8], acc_full[2], acc_empty[2],
 // drain, TMEM base slot, abort flag.
 constexpr int kBarrierBytes = 256;
-__host__ __device__ constexpr int smem_bytes(int bn, int stages) { return stages * stage_bytes(bn) + kBarrierBytes + 1024; }
+__host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1) {
+  return stages * stage_bytes(bn, cg) + kBarrierBytes + 1024;
+}
 __host__ __device__ constexpr int tmem_columns(int bn) { return 2 * bn < 32 ? 32 : 2 * bn; }  // bn is a power of two
 
 struct Waiter {
   volatile uint32_t* abort_flag;
   uint32_t* status;
 
-  // Spin on an mbarrier phase with a time limit.  Returns false when the CTA is aborting.
+  // Wait for an mbarrier phase with a time limit.  Returns false when the CTA is aborting.
+  // The first poll is inline; only a miss pays for the bookkeeping of the bounded spin.
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code, int tile, int kb,
                                        unsigned long long limit_ns = kWaitTimeoutNs) const {
     if (sm100::mbar_try_wait(bar, parity)) return true;
+    return wait_slow(bar, parity, code, tile, kb, limit_ns);
+  }
+
+  __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, uint32_t code, int tile, int kb,
+                                         unsigned long long limit_ns) const {
     const unsigned long long t0 = sm100::globaltimer_ns();
 #pragma unroll 1
     for (uint32_t spin = 1;; ++spin) {
@@ -169,16 +180,27 @@ __device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], boo
   }
 }
 
-template <int BN, typename OutT>
+// CG = 1: one CTA owns a 128 x BN tile.  CG = 2: a CTA pair (cluster of two) owns a 256 x BN
+// tile; CTA r of the pair stages rows [128 r, 128 r + 128) of the A tile and rows
+// [BN/2 r, BN/2 r + BN/2) of the B tile, the leader (r = 0) issues tcgen05.mma.cta_group::2
+// for both, and each CTA ends up with its 128 rows x BN columns of the accumulator in its own
+// tensor memory.  The pair halves the B bytes each SM must stage per flop, which buys deeper
+// rings in the same shared memory.  In the pair, full[] lives in the leader and counts the
+// bytes of both CTAs' copies; empty[] and acc_full[] exist in both CTAs and the leader's
+// commits arrive on each; acc_empty[] lives in the leader and collects both CTAs' epilogues.
+template <int BN, typename OutT, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
   using namespace sm100;
   static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+  static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair");
+  constexpr uint32_t kBRows = BN / CG;  // B rows staged by this CTA
   constexpr uint32_t kABytes = kBM * kRowBytes;
-  constexpr uint32_t kBBytes = BN * kRowBytes;
+  constexpr uint32_t kBBytes = kBRows * kRowBytes;
   constexpr uint32_t kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = tmem_columns(BN);
+  constexpr int kTileM = kBM * CG;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_raw_u32 = smem_u32(smem_raw);
@@ -196,8 +218,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  long long t_cycles = 0;
+  unsigned long long t_ns = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    t_cycles = clock64();
+    t_ns = globaltimer_ns();
+  }
   const Waiter waiter{abort_flag, p.status};
   const int num_items = p.num_tiles * p.split_k;
+  const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;  // position in the pair
+  const bool leader = cta_rank == 0u;
+  const int first_item = static_cast<int>(blockIdx.x) / CG;    // one work item per CTA (pair) at a time
+  const int item_stride = static_cast<int>(gridDim.x) / CG;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
@@ -206,7 +238,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), kEpilogueWarps);
+      mbar_init(acc_empty_bar(a), kEpilogueWarps * CG);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0u;
@@ -215,66 +247,97 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
   }
-  if (warp == 1) tmem_alloc<1>(tmem_slot, kTmemCols);
+  if (warp == 1) tmem_alloc<CG>(tmem_slot, kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (warp == 0) {
     // ------------------------------- producer -------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      long long issued = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-        const int tile = item / p.split_k;
-        const int split = item - tile * p.split_k;
-        int m_blk, n_blk;
-        tile_coords(p, tile, m_blk, n_blk);
-        const int kb0 = split * p.num_kb;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!waiter.wait(empty_bar(stage), phase ^ 1u, kStatusProducerEmptyWait, tile, kb)) {
-            ok = false;
-            break;
-          }
+    // The whole warp walks the loop (every lane polls the barrier); one elected lane issues.
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int item = first_item; ok && item < num_items; item += item_stride) {
+      const int tile = item / p.split_k;
+      const int split = item - tile * p.split_k;
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const int kb0 = split * p.num_kb;
+      const int a_row = m_blk * kTileM + static_cast<int>(cta_rank) * kBM;
+      const int b_row = n_blk * BN + static_cast<int>(cta_rank * kBRows);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!waiter.wait(empty_bar(stage), phase ^ 1u, kStatusProducerEmptyWait, tile, kb)) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
-          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-          tma_load_2d(a_dst, &tmap_a, full_bar(stage), (kb0 + kb) * p.kb_elems, m_blk * kBM);
-          if (p.b_packed != nullptr) {
-            const size_t blk = static_cast<size_t>(n_blk) * (static_cast<size_t>(p.num_kb) * p.split_k) + (kb0 + kb);
-            bulk_load_1d(b_dst, static_cast<const uint8_t*>(p.b_packed) + blk * kBBytes, kBBytes, full_bar(stage));
+          const int k_elem = (kb0 + kb) * p.kb_elems;
+          if (p.debug_mode == 1) {
+            if (leader) mbar_arrive(full_bar(stage));
+          } else if constexpr (CG == 1) {
+            mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+            tma_load_2d(a_dst, &tmap_a, full_bar(stage), k_elem, a_row);
+            if (p.b_packed != nullptr) {
+              const size_t blk = static_cast<size_t>(n_blk) * (static_cast<size_t>(p.num_kb) * p.split_k) + (kb0 + kb);
+              bulk_load_1d(b_dst, static_cast<const uint8_t*>(p.b_packed) + blk * kBBytes, kBBytes, full_bar(stage));
+            } else {
+              tma_load_2d(b_dst, &tmap_b, full_bar(stage), k_elem, b_row);
+            }
           } else {
-            tma_load_2d(b_dst, &tmap_b, full_bar(stage), (kb0 + kb) * p.kb_elems, n_blk * BN);
-          }
-          ++issued;
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
+            // Both CTAs' copies complete on the leader's barrier, which the leader arms with
+            // the byte count of the pair.
+            const uint32_t leader_full = map_to_cta(full_bar(stage), 0u);
+            if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * kStageBytes);
+            tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, a_row);
+            tma_load_2d_pair(b_dst, &tmap_b, leader_full, k_elem, b_row);
           }
         }
+        __syncwarp();
+        ++issued;
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
-      if (!ok) {
-        // Aborting: let the copies already issued land before the CTA may exit.
-        for (int s = 0; s < p.stages; ++s) {
-          if (issued > s) {
-            const long long last = (issued - 1) - ((issued - 1 - s) % p.stages);  // last issue into slot s
-            waiter.wait(full_bar(s), static_cast<uint32_t>((last / p.stages) & 1), 0u, 0, 0, kDrainTimeoutNs);
-          }
+    }
+    if (!ok && leader) {
+      // Aborting: let the copies already issued land before the CTA may exit.
+      for (int s = 0; s < p.stages; ++s) {
+        if (issued > s) {
+          const long long last = (issued - 1) - ((issued - 1 - s) % p.stages);  // last issue into slot s
+          waiter.wait(full_bar(s), static_cast<uint32_t>((last / p.stages) & 1), 0u, 0, 0, kDrainTimeoutNs);
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // ------------------------------- MMA issuer (leader CTA only) -------------------------------
+    if (leader) {
+      // Everything the per-stage path needs is kept in registers and advanced incrementally:
+      // the issuing thread's own instruction latency between two stages is on the critical path.
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+      const uint32_t desc_hi = smem_desc_hi_sw128();
+      const uint32_t a_lo0 = smem_desc_lo(smem_base);
+      const uint32_t b_off = kABytes >> 4;
+      uint32_t a_lo = a_lo0;
+      uint32_t full_addr = full_bar(0);
+      uint32_t empty_addr = empty_bar(0);
+      const uint32_t peer_delta = CG == 2 ? map_to_cta(bar_base, 1u) - bar_base : 0u;  // same offset in the peer CTA
+      const bool do_mma = p.debug_mode != 2;
+      const bool kind_f8 = p.kind_f8 != 0;
+      const uint32_t idesc = p.idesc;
+      const int stages = p.stages;
+      const int num_kb = p.num_kb;
+      for (int item = first_item; ok && item < num_items; item += item_stride) {
         const int tile = item / p.split_k;
         if (!waiter.wait(acc_empty_bar(acc), acc_phase ^ 1u, kStatusMmaAccEmptyWait, tile, 0)) {
           ok = false;
@@ -282,41 +345,50 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!waiter.wait(full_bar(stage), phase, kStatusMmaFullWait, tile, kb)) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!waiter.wait(full_addr, phase, kStatusMmaFullWait, tile, kb)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_src = smem_base + stage * kStageBytes;
-          const uint64_t desc_a = make_smem_desc_sw128(a_src);
-          const uint64_t desc_b = make_smem_desc_sw128(a_src + kABytes);
-#pragma unroll
-          for (int k = 0; k < kMmasPerStage; ++k) {
-            // +32 bytes of K per instruction = +2 in the descriptor's 16-byte address units.
-            umma_ss<1>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u, p.kind_f8 != 0);
+          if (elect_one()) {
+            if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, kind_f8);
+            umma_commit<CG>(empty_addr);
+            if constexpr (CG == 2) umma_commit<CG>(empty_addr + peer_delta);
           }
-          umma_commit<1>(empty_bar(stage));
-          if (++stage == p.stages) {
+          __syncwarp();
+          ++stage;
+          a_lo += kStageBytes >> 4;
+          full_addr += 8u;
+          empty_addr += 8u;
+          if (stage == stages) {
             stage = 0;
             phase ^= 1u;
+            a_lo = a_lo0;
+            full_addr = full_bar(0);
+            empty_addr = empty_bar(0);
           }
         }
         if (!ok) break;
-        umma_commit<1>(acc_full_bar(acc));
+        if (elect_one()) {
+          umma_commit<CG>(acc_full_bar(acc));
+          if constexpr (CG == 2) umma_commit<CG>(acc_full_bar(acc) + peer_delta);
+        }
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
       if (!ok) {
         // Aborting: wait for the MMAs already issued before TMEM and shared memory go away.
-        umma_commit<1>(drain_bar);
+        if (elect_one()) umma_commit<CG>(drain_bar);
+        __syncwarp();
         waiter.wait(drain_bar, 0u, 0u, 0, 0, kDrainTimeoutNs);
       }
     }
   } else {
     // ------------------------------- epilogue -------------------------------
     const int quarter = warp & 3;  // TMEM lanes this warp may read
-    const int row_in_tile = quarter * 32 + lane;
+    const int row_in_tile = static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
     float alpha = 1.0f;
     if (p.scale_a != nullptr) alpha *= __ldg(p.scale_a);
     if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
@@ -325,7 +397,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+    for (int item = first_item; ok && item < num_items; item += item_stride) {
       const int tile = item / p.split_k;
       const int split = item - tile * p.split_k;
       int m_blk, n_blk;
@@ -335,7 +407,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         break;
       }
       tc_fence_after_sync();
-      const int row = m_blk * kBM + row_in_tile;
+      const int row = m_blk * kTileM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
       float bias_row = 0.0f;
@@ -378,7 +450,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      if (lane == 0) {
+        if constexpr (CG == 1) {
+          mbar_arrive(acc_empty_bar(acc));
+        } else {
+          mbar_arrive_remote(map_to_cta(acc_empty_bar(acc), 0u));
+        }
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -387,9 +465,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // ------------------------------- teardown -------------------------------
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const unsigned long long cyc = static_cast<unsigned long long>(clock64() - t_cycles);
+    const unsigned long long ns = globaltimer_ns() - t_ns;
+    p.status[4] = static_cast<uint32_t>(cyc);
+    p.status[5] = static_cast<uint32_t>(cyc >> 32);
+    p.status[6] = static_cast<uint32_t>(ns);
+    p.status[7] = static_cast<uint32_t>(ns >> 32);
   }
 #endif
 }

@@ -70,15 +70,20 @@ int make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t row
 
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const Params);
 
-KernelFn select_kernel(int bn, int dtype_c) {
-  const bool f32 = dtype_c == B200_F32;
+template <int CG>
+KernelFn select_kernel_cg(int bn, bool f32) {
   switch (bn) {
-    case 32: return f32 ? gemm::gemm_tn_kernel<32, float> : gemm::gemm_tn_kernel<32, __nv_bfloat16>;
-    case 64: return f32 ? gemm::gemm_tn_kernel<64, float> : gemm::gemm_tn_kernel<64, __nv_bfloat16>;
-    case 128: return f32 ? gemm::gemm_tn_kernel<128, float> : gemm::gemm_tn_kernel<128, __nv_bfloat16>;
-    case 256: return f32 ? gemm::gemm_tn_kernel<256, float> : gemm::gemm_tn_kernel<256, __nv_bfloat16>;
+    case 32: return f32 ? gemm::gemm_tn_kernel<32, float, CG> : gemm::gemm_tn_kernel<32, __nv_bfloat16, CG>;
+    case 64: return f32 ? gemm::gemm_tn_kernel<64, float, CG> : gemm::gemm_tn_kernel<64, __nv_bfloat16, CG>;
+    case 128: return f32 ? gemm::gemm_tn_kernel<128, float, CG> : gemm::gemm_tn_kernel<128, __nv_bfloat16, CG>;
+    case 256: return f32 ? gemm::gemm_tn_kernel<256, float, CG> : gemm::gemm_tn_kernel<256, __nv_bfloat16, CG>;
     default: return nullptr;
   }
+}
+
+KernelFn select_kernel(int bn, int dtype_c, int cta_group) {
+  const bool f32 = dtype_c == B200_F32;
+  return cta_group == 2 ? select_kernel_cg<2>(bn, f32) : select_kernel_cg<1>(bn, f32);
 }
 
 int elt_bytes(int dtype) {
@@ -154,6 +159,7 @@ std::mutex g_flush_mu;
 struct b200_gemm_plan {
   b200_gemm_desc desc;
   int bn = 0;
+  int cg = 1;         // CTAs per MMA: 1, or 2 for a CTA pair (cluster of two)
   int stages = 0;
   int split_k = 1;
   int grid = 0;
@@ -168,7 +174,7 @@ struct b200_gemm_plan {
   KernelFn kernel = nullptr;
   bool attr_set = false;
   int attr_device = -1;
-  uint32_t* status = nullptr;  // device, 4 words, allocated on first run
+  uint32_t* status = nullptr;  // device, 8 words, allocated on first run
   int status_device = -1;
   // Tensor maps are a pure function of (pointer, shape); cache the last pair.
   const void* map_a_ptr = nullptr;
@@ -206,7 +212,31 @@ int ensure_device_state(b200_gemm_plan* plan) {
     plan->sm_count = sms;
     const int items = plan->m_blocks * plan->n_blocks * plan->split_k;
     int cap = plan->desc.max_ctas > 0 ? plan->desc.max_ctas : sms;
-    plan->grid = items < cap ? items : cap;
+    if (plan->cg == 2) {
+      // Persistent pairs: as many clusters of two as can be resident at once.
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(sms - sms % 2));
+      cfg.blockDim = dim3(gemm::kThreads);
+      cfg.dynamicSmemBytes = static_cast<size_t>(plan->smem);
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, reinterpret_cast<const void*>(plan->kernel), &cfg) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        clusters = sms / 2;
+      }
+      int pairs = cap / 2 < 1 ? 1 : cap / 2;
+      if (pairs > clusters) pairs = clusters;
+      if (pairs > items) pairs = items;
+      plan->grid = 2 * pairs;
+    } else {
+      plan->grid = items < cap ? items : cap;
+    }
     plan->attr_set = true;
     plan->attr_device = dev;
     plan->map_a_ptr = plan->map_b_ptr = nullptr;
@@ -214,8 +244,8 @@ int ensure_device_state(b200_gemm_plan* plan) {
   if (plan->status == nullptr || plan->status_device != dev) {
     if (plan->status != nullptr) cudaFree(plan->status);
     plan->status = nullptr;
-    B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&plan->status), 4 * sizeof(uint32_t)));
-    B200_CUDA_OK(cudaMemset(plan->status, 0, 4 * sizeof(uint32_t)));
+    B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&plan->status), 8 * sizeof(uint32_t)));
+    B200_CUDA_OK(cudaMemset(plan->status, 0, 8 * sizeof(uint32_t)));
     plan->status_device = dev;
   }
   return B200_OK;
@@ -241,7 +271,7 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
            const float* scale_b, void* workspace, cudaStream_t stream) {
   const b200_gemm_desc& d = plan->desc;
   if (plan->map_a_ptr != A) {
-    int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);
+    int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);  // per CTA
     if (rc != B200_OK) return rc;
     plan->map_a_ptr = A;
   }
@@ -250,7 +280,7 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
       plan->map_b = plan->map_a;  // never dereferenced: packed B is streamed with 1-D bulk copies
     } else {
       int rc = make_operand_map(&plan->map_b, B, d.dtype_ab, static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.K),
-                                static_cast<uint32_t>(plan->bn));
+                                static_cast<uint32_t>(plan->bn / plan->cg));
       if (rc != B200_OK) return rc;
     }
     plan->map_b_ptr = B;
@@ -269,7 +299,8 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.stages = plan->stages;
   p.raster_group = plan->raster_group;
   p.kind_f8 = d.dtype_ab == B200_E4M3 ? 1 : 0;
-  p.idesc = sm100::make_idesc(d.dtype_ab == B200_BF16 ? 1u : 0u, gemm::kBM, static_cast<uint32_t>(plan->bn));
+  p.idesc = sm100::make_idesc(d.dtype_ab == B200_BF16 ? 1u : 0u, static_cast<uint32_t>(gemm::kBM * plan->cg),
+                              static_cast<uint32_t>(plan->bn));
   p.relu = (d.epilogue == B200_EPI_BIAS_RELU || d.epilogue == B200_EPI_RELU) ? 1 : 0;
   p.bias_axis = d.bias_axis;
   p.bias = (d.epilogue == B200_EPI_BIAS_RELU || d.epilogue == B200_EPI_BIAS) ? bias : nullptr;
@@ -279,7 +310,24 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.b_packed = direct_b(plan) ? B : nullptr;
   p.workspace = static_cast<float*>(workspace);
   p.status = plan->status;
-  plan->kernel<<<plan->grid, gemm::kThreads, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+  p.debug_mode = d.reserved[0];
+  if (plan->cg == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(plan->grid));
+    cfg.blockDim = dim3(gemm::kThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(plan->smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_OK(cudaLaunchKernelEx(&cfg, plan->kernel, plan->map_a, plan->map_b, p));
+  } else {
+    plan->kernel<<<plan->grid, gemm::kThreads, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+  }
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());
   if (plan->split_k > 1) {
@@ -326,12 +374,19 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
     // Preconditions of the reference's shuffle_weight (kittens_helpers.py:107-108).
     B200_REQUIRE(d.N % 16 == 0 && d.K % 32 == 0, "gemm_plan_create: preshuffled B needs N %% 16 == 0 and K %% 32 == 0");
   }
-  B200_REQUIRE(d.tile_m == 0 || d.tile_m == gemm::kBM, "gemm_plan_create: tile_m=%d unsupported (128)", d.tile_m);
+  B200_REQUIRE(d.tile_m == 0 || d.tile_m == gemm::kBM || d.tile_m == 2 * gemm::kBM,
+               "gemm_plan_create: tile_m=%d unsupported (128, or 256 for a CTA pair)", d.tile_m);
   B200_REQUIRE(d.tile_n == 0 || d.tile_n == 32 || d.tile_n == 64 || d.tile_n == 128 || d.tile_n == 256,
                "gemm_plan_create: tile_n=%d unsupported (32, 64, 128, 256)", d.tile_n);
   const int kb_elems = gemm::kRowBytes / eb;
   B200_REQUIRE(d.tile_k == 0 || d.tile_k == kb_elems, "gemm_plan_create: tile_k=%d unsupported (%d for this dtype)", d.tile_k, kb_elems);
-  B200_REQUIRE(d.cta_group == 0 || d.cta_group == 1, "gemm_plan_create: cta_group=%d unsupported (1)", d.cta_group);
+  B200_REQUIRE(d.cta_group >= 0 && d.cta_group <= 2, "gemm_plan_create: cta_group=%d unsupported (1 or 2)", d.cta_group);
+  B200_REQUIRE(!(d.cta_group == 2 && d.tile_m == gemm::kBM) && !(d.cta_group == 1 && d.tile_m == 2 * gemm::kBM),
+               "gemm_plan_create: tile_m=%d contradicts cta_group=%d (128 rows per CTA)", d.tile_m, d.cta_group);
+  B200_REQUIRE(!(d.b_layout != B200_B_ROW_MAJOR_NK && (d.cta_group == 2 || d.tile_m == 2 * gemm::kBM)),
+               "gemm_plan_create: the direct-B path runs with cta_group=1");
+  B200_REQUIRE(!((d.cta_group == 2 || d.tile_m == 2 * gemm::kBM) && d.tile_n == 32),
+               "gemm_plan_create: a CTA pair needs tile_n >= 64");
   B200_REQUIRE(d.stages >= 0 && d.stages <= gemm::kMaxStages, "gemm_plan_create: stages=%d outside [0,%d]", d.stages, gemm::kMaxStages);
   B200_REQUIRE(d.split_k >= -1 && d.split_k <= 64, "gemm_plan_create: split_k=%d outside [-1,64]", d.split_k);
   B200_REQUIRE(d.max_ctas >= 0 && d.raster_group >= 0, "gemm_plan_create: max_ctas and raster_group must be >= 0");
@@ -342,16 +397,23 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   plan->desc.label[sizeof(plan->desc.label) - 1] = 0;
   plan->eb_ab = eb;
   plan->kb_elems = kb_elems;
-  plan->m_blocks = ceil_div(d.M, gemm::kBM);
   const int k_blocks = ceil_div(d.K, kb_elems);
+
+  // CTA pair or single CTA.  A pair stages half of the B tile per SM, which leaves room for a
+  // deeper ring; it needs at least one full 256-row tile to pay off and row-major B.
+  int cg = d.cta_group != 0 ? d.cta_group : (d.tile_m == 2 * gemm::kBM ? 2 : (d.tile_m == gemm::kBM ? 1 : 0));
+  if (cg == 0) cg = (d.b_layout == B200_B_ROW_MAJOR_NK && d.M >= 2 * gemm::kBM && d.tile_n != 32) ? 2 : 1;
+  plan->cg = cg;
+  plan->m_blocks = ceil_div(d.M, gemm::kBM * cg);
 
   // Tile width: the widest tile whose tile count still fills the machine; wide tiles halve the
   // shared-memory traffic per flop, narrow ones keep more SMs busy on small problems.
   int bn = d.tile_n;
   if (bn == 0) {
+    const int units = kDefaultSms / cg;  // CTAs or pairs that run at once
     bn = 256;
-    while (bn > 64 && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, bn) < kDefaultSms) bn /= 2;
-    while (bn > 32 && bn / 2 >= d.N) bn /= 2;
+    while (bn > 64 && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, bn) < units) bn /= 2;
+    while (bn > (cg == 2 ? 64 : 32) && bn / 2 >= d.N) bn /= 2;
   }
   plan->bn = bn;
   plan->n_blocks = ceil_div(d.N, bn);
@@ -368,23 +430,28 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   plan->num_kb = ceil_div(k_blocks, split);
   plan->total_kb = plan->num_kb * split;
 
-  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024) / gemm::stage_bytes(bn);
+  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024) / gemm::stage_bytes(bn, cg);
   int stages = d.stages > 0 ? d.stages : (max_stages < gemm::kMaxStages ? max_stages : gemm::kMaxStages);
   if (stages > max_stages) {
     delete plan;
     return b200::fail(B200_ERR_INVALID, "gemm_plan_create: %d stages of %d bytes exceed the %d-byte shared memory limit", stages,
-                      gemm::stage_bytes(bn), kMaxSmemOptin);
+                      gemm::stage_bytes(bn, cg), kMaxSmemOptin);
   }
   plan->stages = stages;
-  plan->smem = gemm::smem_bytes(bn, stages);
+  plan->smem = gemm::smem_bytes(bn, stages, cg);
   // Two resident CTAs would both ask for TMEM; keep the footprint above half the SM's shared
   // memory whenever two allocations (2 * tmem_columns) would not fit in the 512 columns.
   if (2 * gemm::tmem_columns(bn) > 512 && plan->smem <= kMaxSmemOptin / 2) plan->smem = kMaxSmemOptin / 2 + 1024;
   plan->raster_group = d.raster_group > 0 ? d.raster_group : 8;
-  plan->kernel = select_kernel(bn, d.dtype_c);
+  plan->kernel = select_kernel(bn, d.dtype_c, cg);
   const int items = plan->m_blocks * plan->n_blocks * plan->split_k;
   const int cap = d.max_ctas > 0 ? d.max_ctas : kDefaultSms;
-  plan->grid = items < cap ? items : cap;
+  if (cg == 2) {
+    int pairs = cap / 2 < 1 ? 1 : cap / 2;
+    plan->grid = 2 * (items < pairs ? items : pairs);
+  } else {
+    plan->grid = items < cap ? items : cap;
+  }
   *out = plan;
   return B200_OK;
 }
@@ -400,11 +467,11 @@ int b200_gemm_plan_destroy(b200_gemm_plan* plan) {
 int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* out) {
   B200_REQUIRE(plan != nullptr && out != nullptr, "gemm_plan_resources: NULL argument");
   std::memset(out, 0, sizeof(*out));
-  out->tile_m = gemm::kBM;
+  out->tile_m = gemm::kBM * plan->cg;
   out->tile_n = plan->bn;
   out->tile_k = plan->kb_elems;
   out->stages = plan->stages;
-  out->cta_group = 1;
+  out->cta_group = plan->cg;
   out->split_k = plan->split_k;
   out->grid_ctas = plan->grid;
   out->block_threads = gemm::kThreads;
@@ -507,6 +574,19 @@ int b200_status_read(b200_gemm_plan* plan, uint32_t words[4]) {
     return b200::fail(B200_ERR_TIMEOUT, "device wait timed out: code 0x%x cta %u tile %u k-block %u", words[0], words[1], words[2],
                       words[3]);
   }
+  return B200_OK;
+}
+
+int b200_gemm_last_sm_mhz(b200_gemm_plan* plan, float* mhz) {
+  B200_REQUIRE(plan != nullptr && mhz != nullptr, "gemm_last_sm_mhz: NULL argument");
+  *mhz = 0.0f;
+  if (plan->status == nullptr) return B200_OK;
+  B200_CUDA_OK(cudaDeviceSynchronize());
+  uint32_t w[8];
+  B200_CUDA_OK(cudaMemcpy(w, plan->status, sizeof(w), cudaMemcpyDeviceToHost));
+  const double cycles = static_cast<double>((static_cast<uint64_t>(w[5]) << 32) | w[4]);
+  const double ns = static_cast<double>((static_cast<uint64_t>(w[7]) << 32) | w[6]);
+  if (ns > 0) *mhz = static_cast<float>(cycles / ns * 1000.0);
   return B200_OK;
 }
 

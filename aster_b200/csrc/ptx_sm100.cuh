@@ -11,6 +11,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// True in exactly one lane of a fully converged warp (the same lane every time).  Code that
+// issues TMA or tcgen05 instructions from one thread runs its loops warp-uniformly and guards
+// only the issue with this, so the compiler sees a converged warp around the instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -35,17 +50,30 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Arrive on the barrier at the same shared-memory offset in CTA `cta_rank` of this cluster.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t local_bar, uint32_t cta_rank) {
-  asm volatile(
-      "{\n"
-      ".reg .b32 remote;\n"
-      "mapa.shared::cluster.u32 remote, %0, %1;\n"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n"
-      "}\n" ::"r"(local_bar),
-      "r"(cta_rank)
-      : "memory");
+// shared::cluster address of the location at this CTA's shared-memory address `local_addr`
+// inside CTA `cta_rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  return remote;
 }
+// Arrive on a barrier given by a shared::cluster address (this CTA's or a peer's).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Cluster-wide barrier over all threads of all CTAs (release/acquire).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One poll of the barrier's phase (the hardware may park the thread briefly before answering).
+// A longer suspend hint or single-lane polling was measured slower: the wake-up latency lands
+// on the critical path of the MMA issue loop.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -182,6 +210,66 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64
     }
   }
 }
+
+// The four MMAs of one pipeline stage in a single instruction sequence: D (+)= A_k . B_k^T for
+// the four 32-byte K slices of a 128-byte-swizzled stage.  `a_lo` / `b_lo` are the low words of
+// the operands' shared-memory descriptors (start address >> 4 | LBO), `desc_hi` their common
+// high word; each slice advances the low word by 2 (32 bytes).  `accumulate_first` = 0 makes
+// the first MMA overwrite D.  Kept as one asm block so that nothing but two adds and two moves
+// separates consecutive tcgen05.mma: the issuing thread's instruction latency between MMAs is
+// what starves the tensor pipe otherwise.
+#define B200_MMA_STAGE_ASM(GROUP, KIND)                                                         \
+  asm volatile(                                                                                 \
+      "{\n"                                                                                     \
+      ".reg .pred p, q;\n"                                                                      \
+      ".reg .b64 da, db;\n"                                                                     \
+      ".reg .b32 la, lb;\n"                                                                     \
+      "setp.ne.b32 p, %5, 0;\n"                                                                 \
+      "setp.eq.b32 q, 0, 0;\n"                                                                  \
+      "mov.b64 da, {%1, %3};\n"                                                                 \
+      "mov.b64 db, {%2, %3};\n"                                                                 \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n"                  \
+      "add.u32 la, %1, 2;\n"                                                                    \
+      "add.u32 lb, %2, 2;\n"                                                                    \
+      "mov.b64 da, {la, %3};\n"                                                                 \
+      "mov.b64 db, {lb, %3};\n"                                                                 \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, q;\n"                  \
+      "add.u32 la, %1, 4;\n"                                                                    \
+      "add.u32 lb, %2, 4;\n"                                                                    \
+      "mov.b64 da, {la, %3};\n"                                                                 \
+      "mov.b64 db, {lb, %3};\n"                                                                 \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, q;\n"                  \
+      "add.u32 la, %1, 6;\n"                                                                    \
+      "add.u32 lb, %2, 6;\n"                                                                    \
+      "mov.b64 da, {la, %3};\n"                                                                 \
+      "mov.b64 db, {lb, %3};\n"                                                                 \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, q;\n"                  \
+      "}\n" ::"r"(tmem_d),                                                                      \
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)                     \
+      : "memory")
+
+template <int CTA_GROUP>
+__device__ __forceinline__ void umma_stage(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                           uint32_t accumulate_first, bool kind_f8) {
+  if constexpr (CTA_GROUP == 1) {
+    if (kind_f8) {
+      B200_MMA_STAGE_ASM("1", "f8f6f4");
+    } else {
+      B200_MMA_STAGE_ASM("1", "f16");
+    }
+  } else {
+    if (kind_f8) {
+      B200_MMA_STAGE_ASM("2", "f8f6f4");
+    } else {
+      B200_MMA_STAGE_ASM("2", "f16");
+    }
+  }
+}
+#undef B200_MMA_STAGE_ASM
+
+// Low / high words of make_smem_desc_sw128 (the high word does not depend on the address).
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ constexpr uint32_t smem_desc_hi_sw128() { return (1024u >> 4) | (1u << 14) | (2u << 29); }
 
 // Make `bar` (a shared::cluster address) complete one arrival once every tcgen05 operation
 // previously issued by this thread has finished.

@@ -60,6 +60,7 @@ class GemmPlan:
         max_ctas: int = 0,
         raster_group: int = 0,
         label: str = "",
+        debug_mode: int = 0,
     ) -> None:
         self._handle = None
         desc = nat.GemmDesc()
@@ -75,6 +76,7 @@ class GemmPlan:
         desc.tile_m, desc.tile_n, desc.tile_k = tile_m, tile_n, tile_k
         desc.stages, desc.cta_group, desc.split_k = stages, cta_group, split_k
         desc.max_ctas, desc.raster_group = max_ctas, raster_group
+        desc.reserved[0] = debug_mode  # kernel bring-up aid: 1 = no copies, 2 = no multiplies (results are garbage)
         desc.label = label.encode()[:255]
         handle = C.c_void_p()
         nat.call("b200_gemm_plan_create", C.byref(desc), C.byref(handle))
@@ -149,6 +151,12 @@ class GemmPlan:
             _ptr(workspace), workspace_bytes, iters, C.byref(ms),
         )
         return ms.value
+
+    def last_sm_mhz(self) -> float:
+        """SM clock (MHz) the last launch actually ran at (cycles / nanoseconds of CTA 0)."""
+        mhz = C.c_float(0.0)
+        nat.call("b200_gemm_last_sm_mhz", self.handle, C.byref(mhz))
+        return mhz.value
 
     def status(self) -> Sequence[int]:
         """Device status words of the last launch; raises ``B200Error`` (TIMEOUT) if a wait gave up."""

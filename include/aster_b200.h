@@ -180,6 +180,10 @@ int b200_gemm_time_batch(b200_gemm_plan* plan, const void* A, const void* B, voi
  * words[0] = 0 when every bounded wait completed; otherwise a code naming the wait that gave
  * up (role, barrier, tile).  Returns B200_ERR_TIMEOUT when words[0] != 0. */
 int b200_status_read(b200_gemm_plan* plan, uint32_t words[4]);
+/* SM clock (MHz) that the plan's last launch actually ran at: cycles over nanoseconds that
+ * CTA 0 spent in the kernel (synchronises the device).  0 if the plan was never launched.
+ * Per-launch tracing in the spirit of the reference's s_memtime cycle counters (README.md:273). */
+int b200_gemm_last_sm_mhz(b200_gemm_plan* plan, float* mhz);
 /* Number of kernel launches issued by this library on the calling process so far. */
 int b200_launch_count(int64_t* count);
 

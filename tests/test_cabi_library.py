@@ -62,8 +62,12 @@ def test_version_and_error_text(native_lib):
     (dict(M=64, N=64, K=24, dtype_ab="e4m3"), "multiple of 16 bytes"),
     (dict(M=64, N=64, K=64, tile_n=48), "tile_n=48"),
     (dict(M=64, N=64, K=64, tile_m=64), "tile_m=64"),
+    (dict(M=512, N=64, K=64, tile_m=128, cta_group=2), "contradicts"),
+    (dict(M=512, N=64, K=64, cta_group=2, tile_n=32), "tile_n >= 64"),
+    (dict(M=512, N=64, K=64, cta_group=2, b_layout="packed"), "cta_group=1"),
     (dict(M=64, N=64, K=64, stages=9), "stages=9"),
     (dict(M=64, N=64, K=64, tile_n=256, stages=5), "shared memory limit"),
+    (dict(M=512, N=512, K=64, tile_n=256, stages=8, cta_group=2), "shared memory limit"),
     (dict(M=64, N=64, K=64, cta_group=3), "cta_group=3"),
     (dict(M=64, N=40, K=64, b_layout="ref_preshuffled"), "preshuffled"),
     (dict(M=64, N=64, K=64, split_k=65), "split_k"),
@@ -87,19 +91,21 @@ def test_plan_enum_validation(native_lib):
 def test_plan_resources_without_a_gpu(native_lib):
     p = GemmPlan(4096, 4096, 4096, "bf16", "bf16")
     r = p.resources()
-    assert (r.tile_m, r.tile_n, r.tile_k, r.block_threads) == (128, 256, 64, 192)
-    assert r.num_tiles == 32 * 16 and r.grid_ctas == 148 and r.tmem_columns == 512
+    assert (r.tile_m, r.tile_n, r.tile_k, r.block_threads, r.cta_group) == (256, 256, 64, 192, 2)
+    assert r.num_tiles == 16 * 16 and r.grid_ctas == 148 and r.tmem_columns == 512 and r.stages == 7
+    single = GemmPlan(4096, 4096, 4096, "bf16", "bf16", cta_group=1).resources()
+    assert (single.tile_m, single.cta_group, single.num_tiles, single.stages) == (128, 1, 32 * 16, 4)
     assert r.smem_bytes <= 232448 and r.ctas_per_sm == 1 and r.workspace_bytes == 0 and r.packed_b_bytes == 0
     p.destroy()
     p.destroy()  # idempotent
     small = GemmPlan(512, 512, 512).resources()
-    assert small.tile_n == 64 and small.num_tiles == 32
+    assert small.tile_n == 64 and small.num_tiles == 16 and small.cta_group == 2 and small.grid_ctas == 32
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()
     assert fp8.tile_k == 128
     skinny = GemmPlan(16, 8192, 8192, "bf16", "bf16", split_k=-1, tile_n=64).resources()
     assert skinny.split_k >= 1 and skinny.workspace_bytes == skinny.split_k * 16 * 8192 * 4 * (skinny.split_k > 1)
     packed = GemmPlan(256, 300 * 16, 512, b_layout="packed", tile_n=256).resources()
-    assert packed.packed_b_bytes == 19 * 256 * 8 * 128
+    assert packed.packed_b_bytes == 19 * 256 * 8 * 128 and packed.cta_group == 1
 
 
 def test_run_argument_checks_do_not_need_a_gpu(native_lib):

@@ -203,6 +203,40 @@ class TestShapesAndTypes:
         assert not gemm(a, a).any()
 
 
+class TestCtaPair:
+    """One CTA per tile (cta_group 1) against a CTA pair per 256-row tile (cta_group 2)."""
+
+    @pytest.mark.parametrize("cta_group", [1, 2])
+    @pytest.mark.parametrize("tile_n", [64, 128, 256])
+    @pytest.mark.parametrize("shape", [(256, 256, 256), (640, 768, 320), (300, 200, 264), (1024, 512, 2048)])
+    def test_tile_shapes(self, gpu, cta_group, tile_n, shape):
+        run(*shape, "bf16", "f32", "uniform", 1, cta_group=cta_group, tile_n=tile_n)
+
+    @pytest.mark.parametrize("dtype_ab,dtype_c", [("f16", "f32"), ("bf16", "bf16"), ("e4m3", "bf16")])
+    def test_pair_equals_single_bitwise(self, gpu, dtype_ab, dtype_c):
+        inp = orc.make_inputs(768, 512, 1024, dtype_ab, "normal", 5)
+        kw = dict(dtype_ab=dtype_ab, dtype_c=dtype_c, scale_a=inp["scale_a"], scale_b=inp["scale_b"], tile_n=128)
+        assert np.array_equal(gemm(inp["A"], inp["B"], cta_group=1, **kw), gemm(inp["A"], inp["B"], cta_group=2, **kw))
+
+    @pytest.mark.parametrize("stages", [1, 2, 4, 7])
+    def test_pair_ring_depths(self, gpu, stages):
+        run(512, 512, 2048, "bf16", "f32", "uniform", 1, cta_group=2, tile_n=256, stages=stages)
+
+    @pytest.mark.parametrize("max_ctas", [2, 6, 148])
+    def test_pair_persistent_grid(self, gpu, max_ctas):
+        run(2048, 1024, 256, "bf16", "bf16", "uniform", 1, cta_group=2, tile_n=128, max_ctas=max_ctas)
+
+    def test_pair_epilogue_and_split_k(self, gpu):
+        run(512, 1024, 256, "bf16", "bf16", "normal", 2, bias=True, relu=True, cta_group=2)
+        run(512, 1024, 256, "bf16", "bf16", "normal", 2, bias=True, relu=True, bias_axis="m", cta_group=2)
+        run(256, 1024, 4096, "bf16", "bf16", "uniform", 4, split_k=4, tile_n=64, cta_group=2)
+
+    def test_odd_row_count_in_pair(self, gpu):
+        # 129..255 rows: the second CTA of the pair owns a partly or wholly empty half.
+        for m in (129, 200, 255, 257, 385):
+            run(m, 192, 128, "bf16", "bf16", "uniform", m, cta_group=2, tile_n=64)
+
+
 class TestEpilogue:
     @pytest.mark.parametrize("dtype_c", ["f32", "bf16"])
     @pytest.mark.parametrize("bias,relu", [(True, True), (True, False), (False, True)])
