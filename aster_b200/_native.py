@@ -145,6 +145,7 @@ SIGNATURES = {
     "b200_gemm_run": [_P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P],
     "b200_gemm_time": [_P, _P, _P, _P, _P, _P, _P, _P, _SZ, C.c_int, C.c_int, _FP],
     "b200_gemm_time_batch": [_P, _P, _P, _P, _P, _P, _P, _P, _SZ, C.c_int, _FP],
+    "b200_gemm_splitk_noalloc": [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, _P],
     "b200_status_read": [_P, C.POINTER(C.c_uint32)],
     "b200_gemm_last_sm_mhz": [_P, _FP],
     "b200_launch_count": [C.POINTER(C.c_int64)],

@@ -165,6 +165,20 @@ class GemmPlan:
         return list(words)
 
 
+def gemm_splitk_noalloc(A, B, Cbuf, M: int, N: int, K: int, dtype_ab: str = "bf16", dtype_c: str = "bf16",
+                        split_k: int = 4, stream=None) -> None:
+    """Enqueue a split-K GEMM whose partial sums live in the library's built-in 16 MiB scratch.
+
+    For hosts that cannot allocate device memory when they need the GEMM (their own pool owns
+    all of it, or they cannot afford the synchronisation an allocation implies).  ``A``, ``B``,
+    ``Cbuf`` are device addresses.  ``split_k * M * N * 4`` must not exceed 16 MiB.  Calls on
+    one device share the scratch: keep them ordered on one stream.  The first call per device
+    performs a one-time host-side set-up and should be made before any stream capture starts.
+    """
+    nat.call("b200_gemm_splitk_noalloc", _ptr(A), _ptr(B), _ptr(Cbuf), int(M), int(N), int(K), DTYPE_CODES[dtype_ab],
+             DTYPE_CODES[dtype_c], int(split_k), _ptr(stream))
+
+
 def _check_operand(name: str, arr: np.ndarray, shape, dtype: str) -> np.ndarray:
     want = STORAGE[dtype]
     if not isinstance(arr, np.ndarray):

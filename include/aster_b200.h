@@ -187,6 +187,24 @@ int b200_gemm_last_sm_mhz(b200_gemm_plan* plan, float* mhz);
 /* Number of kernel launches issued by this library on the calling process so far. */
 int b200_launch_count(int64_t* count);
 
+/* Split-K GEMM that allocates nothing: C[M,N] = A[M,K] . B[N,K]^T with the fp32 partial sums
+ * kept in a 16 MiB scratch array built into the library image instead of a caller workspace.
+ * (No counterpart in the reference; it exists for hosts that cannot call cudaMalloc at GEMM
+ * time: all device memory already belongs to their own pool, or an allocation's device-wide
+ * synchronisation is not acceptable on their path.)
+ *  - A, B, C: device pointers, 16-byte aligned, row-major, K contiguous in A and B.
+ *  - dtype_ab: B200_F16 | B200_BF16 | B200_E4M3; dtype_c: B200_F32 | B200_BF16; no epilogue.
+ *  - split_k in [1, 64] partitions of K (clamped to the number of 128-byte K blocks).
+ *  - Limit: split_k * M * N * 4 bytes <= 16 MiB, else B200_ERR_WORKSPACE (use b200_gemm_run
+ *    with your own workspace for larger problems).
+ *  - The scratch is shared by all calls on a device and keeps the last call's contents; calls
+ *    that overlap on the GPU race on it, so order them on one stream.
+ *  - The first call on each device does a one-time host-side set-up (address lookup of the
+ *    built-in array, kernel attributes); make it before any stream capture begins.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                             int32_t dtype_ab, int32_t dtype_c, int32_t split_k, void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* Bandwidth kernels                                                                          */
 /* ------------------------------------------------------------------------------------------ */
