@@ -56,6 +56,8 @@ WORKLOADS = {
     "decode_128": dict(M=128, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, split_k=-1, tile_n=64, hbm=True,
                        text="bf16 skinny GEMM M=128 N=K=8192, U(-1,1) seed 4"),
     "vector_add": dict(n=1 << 28, text="int32 vector_add, 2^28 elements per array, integers from default_rng(5)"),
+    "vector_add_64m": dict(n=1 << 26, text="int32 vector_add, 2^26 elements per array (profiling size), integers from default_rng(5)"),
+    "copy_2d_padded_8k": dict(M=8192, N=8188, text="fp32 copy_2d_padded 8192x8188 (profiling size), standard normal from default_rng(6)"),
     "copy_2d_padded": dict(M=16384, N=16380, text="fp32 copy_2d_padded 16384x16380 (ragged last column tile), standard normal from default_rng(6)"),
 }
 DEFAULT_WORKLOAD = "bf16_4096"
@@ -233,6 +235,7 @@ def cpu_gemm_seconds(w: dict, rows: int, max_seconds: float, max_reps: int):
     reps, rows used)."""
     from oracle import gemm_oracle as orc
 
+    use_all_host_threads()
     rows = min(rows, w["M"])
     ops = host_operands(w, 0, rows)
     a32 = orc.decode(ops["A"], w["dtype_ab"])
@@ -249,6 +252,18 @@ def cpu_gemm_seconds(w: dict, rows: int, max_seconds: float, max_reps: int):
     return best, reps, rows
 
 
+def use_all_host_threads() -> None:
+    """Let the BLAS behind numpy use every core (torchrun pins OMP_NUM_THREADS=1 for its
+    children; the reference's bench scripts set the thread count to all cores,
+    bench_perf_102_gemm_python_multitile_lds_cdna3.py:24-25)."""
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=os.cpu_count() or 1)
+    except Exception:
+        pass
+
+
 def cpu_threads() -> int:
     try:
         from threadpoolctl import threadpool_info
@@ -263,8 +278,9 @@ def cpu_threads() -> int:
 
 def run_reference_arm(args, w: dict, name: str) -> dict:
     """--impl reference: every step is the numpy GEMM on a bounded row sample."""
+    use_all_host_threads()
     cores = cpu_threads()
-    if "n" in w or name == "copy_2d_padded":
+    if "K" not in w:
         return {"impl": "reference", "unavailable": "bandwidth workloads have no reference arm here; use the GEMM workloads"}
     # Size the sample so the whole run stays within a couple of minutes.
     probe_rows = min(w["M"], 512)
@@ -466,7 +482,7 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
     from aster_b200.gemm import PinnedArray
 
     peaks = measured_peaks()
-    if name == "vector_add":
+    if "n" in w:
         n = w["n"]
         rng = np.random.default_rng(5 + job.rank)
         a = rng.integers(-(2**30), 2**30, n, dtype=np.int64).astype(np.int32)
@@ -518,7 +534,7 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
     line = {
         "metric": "bandwidth_gbs", "value": gbs * job.world, "unit": "GB/s", "n_gpus": job.world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int32" if name == "vector_add" else "f32", "data": "synthetic", "impl": "ours",
+        "dtype": "int32" if "n" in w else "f32", "data": "synthetic", "impl": "ours",
         "config": {"workload": w["text"], "name": name, "l2": f"{alg_bytes / 2**20:.0f} MiB touched per step > {L2_BYTES / 1e6:.0f} MB L2"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                      "peak_source": f"{peaks['_source']} (hbm copy)", "traffic": TRAFFIC_BYTES.get(name), "frac_of_nominal": gbs / 8000.0},
@@ -532,7 +548,7 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
         best = float("inf")
         for _ in range(3):
             c0 = time.perf_counter()
-            _ = orc.vector_add(*host_in) if name == "vector_add" else orc.copy_2d_padded(host_in[0], out)
+            _ = orc.vector_add(*host_in) if "n" in w else orc.copy_2d_padded(host_in[0], out)
             best = min(best, time.perf_counter() - c0)
         line["cpu_baseline"] = {"value": alg_bytes / best / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
                                 "sample": f"whole workload, best of 3 ({best:.3f} s), numpy"}
@@ -541,7 +557,9 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
 
 # DRAM bytes (read + write) per launch of the dominant kernel from the ncu captures summarised
 # under profiles/ (null where no capture exists for the workload).
-TRAFFIC_BYTES: dict = {}
+TRAFFIC_BYTES: dict = {
+    "bf16_4096": 99.4e6,  # profiles/gemm_tn_kernel_bf16_4096.md: 85.4 MB read + 14.0 MB written per launch
+}
 
 
 def main() -> int:
@@ -569,7 +587,7 @@ def main() -> int:
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     nat.call("b200_init", job.local_rank)
     try:
-        if "n" in w or args.workload == "copy_2d_padded":
+        if "K" not in w:
             line = run_bandwidth(args, job, w, args.workload)
         else:
             line = run_gemm(args, job, w, args.workload)
