@@ -101,6 +101,9 @@ class GemmResources(C.Structure):
         ("num_tiles", C.c_int64),
         ("workspace_bytes", C.c_int64),
         ("packed_b_bytes", C.c_int64),
+        ("optional_workspace_bytes", C.c_int64),
+        ("tail_tiles", C.c_int32),
+        ("tail_parts", C.c_int32),
     ]
 
 

@@ -53,6 +53,7 @@ enum : uint32_t {
   kStatusMmaFullWait = 0x20,
   kStatusMmaAccEmptyWait = 0x21,
   kStatusEpilogueAccFullWait = 0x30,
+  kStatusTailFlagWait = 0x31,
 };
 
 struct Params {
@@ -75,6 +76,17 @@ struct Params {
   const void* b_packed;  // non-null: B comes as packed tile images, streamed with 1-D bulk copies
   float* workspace;      // split-K partial sums [split][M][N] fp32
   uint32_t* status;
+  // Tail split: when the last round of tiles would leave most units idle, each of the
+  // `tail_tiles` last tiles is cut into `tail_parts` K ranges handled by different units; part 0
+  // owns the tile and adds the other parts' fp32 partial tiles (exchanged through `tail_ws`,
+  // announced through `tail_flags` = epoch) before its epilogue.  tail_parts <= 1: off.
+  int tail_tiles;
+  int tail_parts;
+  int tail_kb0;           // K blocks of part 0 (the owner: a few more, so that the others finish first)
+  int tail_kb;            // K blocks of every other part
+  float* tail_ws;         // [tail_tiles][tail_parts - 1][tile rows][BN] fp32
+  uint32_t* tail_flags;   // [tail_tiles][tail_parts - 1][CG][4 epilogue warps]
+  uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
   int debug_mode;  // 0 = normal; 1 = producer signals without copying; 2 = MMA warp commits without multiplying
 };
 
@@ -121,6 +133,40 @@ struct Waiter {
   }
 };
 
+// Bounded wait of a whole warp for a global-memory flag written by another CTA of the same
+// launch.  Only lane 0 polls (with a short sleep between polls): dozens of warps hammering the
+// same L2 line delay the very store they are waiting for.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, const Waiter& waiter, int tile) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0 && sm100::ld_acquire_gpu(flag) != want) {
+    const unsigned long long t0 = sm100::globaltimer_ns();
+#pragma unroll 1
+    for (uint32_t spin = 1;; ++spin) {
+      __nanosleep(64);
+      if (sm100::ld_acquire_gpu(flag) == want) break;
+      if ((spin & 63u) == 0u) {
+        if (*waiter.abort_flag != 0u) {
+          ok = 0;
+          break;
+        }
+        if (sm100::globaltimer_ns() - t0 > kWaitTimeoutNs) {
+          if (atomicCAS(waiter.status, 0u, static_cast<uint32_t>(kStatusTailFlagWait)) == 0u) {
+            waiter.status[1] = blockIdx.x;
+            waiter.status[2] = static_cast<uint32_t>(tile);
+            waiter.status[3] = 0u;
+          }
+          *waiter.abort_flag = 1u;
+          ok = 0;
+          break;
+        }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __threadfence();  // the other lanes' reads of the partial tile come after lane 0's acquire
+  return ok != 0;
+}
+
 // Work item -> (m block, n block).  Groups of `raster_group` m-blocks are walked m-fastest so
 // that the ~148 tiles in flight share a few A row panels and B row panels in L2.
 __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m_blk, int& n_blk) {
@@ -131,6 +177,54 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m_bl
   const int in_group = tile - group * group_span;
   m_blk = first_m + in_group % rows;
   n_blk = in_group / rows;
+}
+
+// One unit of work for a CTA (pair): a tile, a K range of it, and what to do with the result.
+struct WorkItem {
+  int tile;
+  int kb0;    // first K block
+  int nkb;    // K blocks to accumulate
+  int split;  // split-K partition (results go to the split-K workspace), 0 otherwise
+  int part;   // tail split: -1 = whole tile, 0 = owner, > 0 = contributor
+  int tail_index;  // index of the tile among the tail tiles
+};
+
+__device__ __forceinline__ int num_work_items(const Params& p) {
+  if (p.split_k > 1) return p.num_tiles * p.split_k;
+  return p.tail_parts > 1 ? p.num_tiles - p.tail_tiles + p.tail_tiles * p.tail_parts : p.num_tiles;
+}
+
+__device__ __forceinline__ WorkItem decode_item(const Params& p, int item) {
+  WorkItem w;
+  w.split = 0;
+  w.part = -1;
+  w.tail_index = 0;
+  if (p.split_k > 1) {
+    w.tile = item / p.split_k;
+    w.split = item - w.tile * p.split_k;
+    w.kb0 = w.split * p.num_kb;
+    w.nkb = p.num_kb;
+    return w;
+  }
+  const int whole = p.tail_parts > 1 ? p.num_tiles - p.tail_tiles : p.num_tiles;
+  if (item < whole) {
+    w.tile = item;
+    w.kb0 = 0;
+    w.nkb = p.num_kb;
+    return w;
+  }
+  const int t = item - whole;
+  w.tail_index = t / p.tail_parts;
+  w.part = t - w.tail_index * p.tail_parts;
+  w.tile = whole + w.tail_index;
+  if (w.part == 0) {
+    w.kb0 = 0;
+    w.nkb = p.tail_kb0;
+  } else {
+    w.kb0 = p.tail_kb0 + (w.part - 1) * p.tail_kb;
+    w.nkb = min(p.tail_kb, p.num_kb - w.kb0);
+  }
+  return w;
 }
 
 template <typename OutT>
@@ -225,7 +319,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     t_ns = globaltimer_ns();
   }
   const Waiter waiter{abort_flag, p.status};
-  const int num_items = p.num_tiles * p.split_k;
+  const int num_items = num_work_items(p);
   const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;  // position in the pair
   const bool leader = cta_rank == 0u;
   const int first_item = static_cast<int>(blockIdx.x) / CG;    // one work item per CTA (pair) at a time
@@ -262,14 +356,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     long long issued = 0;
     bool ok = true;
     for (int item = first_item; ok && item < num_items; item += item_stride) {
-      const int tile = item / p.split_k;
-      const int split = item - tile * p.split_k;
+      const WorkItem w = decode_item(p, item);
+      const int tile = w.tile;
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
-      const int kb0 = split * p.num_kb;
+      const int kb0 = w.kb0;
       const int a_row = m_blk * kTileM + static_cast<int>(cta_rank) * kBM;
       const int b_row = n_blk * BN + static_cast<int>(cta_rank * kBRows);
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      for (int kb = 0; kb < w.nkb; ++kb) {
         if (!waiter.wait(empty_bar(stage), phase ^ 1u, kStatusProducerEmptyWait, tile, kb)) {
           ok = false;
           break;
@@ -278,7 +372,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const int k_elem = (kb0 + kb) * p.kb_elems;
-          if (p.debug_mode == 1) {
+          if ((p.debug_mode & 3) == 1) {
             if (leader) mbar_arrive(full_bar(stage));
           } else if constexpr (CG == 1) {
             mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
@@ -332,13 +426,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t full_addr = full_bar(0);
       uint32_t empty_addr = empty_bar(0);
       const uint32_t peer_delta = CG == 2 ? map_to_cta(bar_base, 1u) - bar_base : 0u;  // same offset in the peer CTA
-      const bool do_mma = p.debug_mode != 2;
+      const bool do_mma = (p.debug_mode & 3) != 2;
       const bool kind_f8 = p.kind_f8 != 0;
       const uint32_t idesc = p.idesc;
       const int stages = p.stages;
-      const int num_kb = p.num_kb;
       for (int item = first_item; ok && item < num_items; item += item_stride) {
-        const int tile = item / p.split_k;
+        const WorkItem w = decode_item(p, item);
+        const int tile = w.tile;
+        const int num_kb = w.nkb;
         if (!waiter.wait(acc_empty_bar(acc), acc_phase ^ 1u, kStatusMmaAccEmptyWait, tile, 0)) {
           ok = false;
           break;
@@ -398,8 +493,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int item = first_item; ok && item < num_items; item += item_stride) {
-      const int tile = item / p.split_k;
-      const int split = item - tile * p.split_k;
+      const WorkItem w = decode_item(p, item);
+      const int tile = w.tile;
+      const int split = w.split;
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
       if (!waiter.wait(acc_full_bar(acc), acc_phase, kStatusEpilogueAccFullWait, tile, 0)) {
@@ -412,6 +508,33 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
       float bias_row = 0.0f;
       if (p.bias != nullptr && p.bias_axis == 1 && row_ok) bias_row = __ldg(p.bias + row);
+      // Tail split: partial tiles travel in "register image" order -- for each 32-column chunk,
+      // float4 j of lane l sits at [warp slab][chunk][j][l] -- because the contributor and the
+      // owner use the same lane <-> (row, column) mapping.  Every exchange access is therefore a
+      // fully coalesced 512-byte warp access; a row-major exchange was 8x slower end to end.
+      const size_t tail_tile_elems = static_cast<size_t>(kTileM) * BN;
+      const int flag_lane = (static_cast<int>(cta_rank) * 4 + quarter);
+      const size_t warp_slab = static_cast<size_t>(flag_lane) * (32u * BN);  // floats per warp = 32 rows x BN
+      const bool exchange = (p.debug_mode & 4) == 0;
+      if (w.part == 0 && exchange) {
+        // Owner: the contributors' partial sums for these 32 rows must have landed.
+        for (int q = 1; q < p.tail_parts; ++q) {
+          const uint32_t* flag = p.tail_flags + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (q - 1)) * (CG * 4) + flag_lane;
+          if (!wait_flag(flag, p.epoch, waiter, tile)) {
+            ok = false;
+            break;
+          }
+        }
+        if (!ok) break;
+      }
+      // Owner: this lane's float4 column of the first contributor's partial tile, chunk 0 loaded now.
+      const float4* tail_src = reinterpret_cast<const float4*>(
+                                   p.tail_ws + static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) * tail_tile_elems + warp_slab) + lane;
+      float4 ahead[8];
+      if (w.part == 0 && exchange) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + j * 32);
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
@@ -431,8 +554,49 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           continue;
         }
+        if (w.part > 0) {
+          // Contributor: hand the raw fp32 tile to the owner (whole rows, ragged edges included).
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) * alpha;
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+          float4* wdst = reinterpret_cast<float4*>(p.tail_ws + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (w.part - 1)) * tail_tile_elems +
+                                                   warp_slab + static_cast<size_t>(c) * 32u) + lane;
+          if (exchange) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wdst[j * 32] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+          }
+          continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+        if (w.part == 0 && exchange) {
+          // The first contributor's chunk was fetched one iteration ahead (`ahead`); further
+          // contributors, if any, are read in place.
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            x[4 * j] += ahead[j].x;
+            x[4 * j + 1] += ahead[j].y;
+            x[4 * j + 2] += ahead[j].z;
+            x[4 * j + 3] += ahead[j].w;
+          }
+          if (c + 32 < BN) {
+            const float4* nxt = tail_src + static_cast<size_t>(c + 32) * 8u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(nxt + j * 32);
+          }
+          for (int q = 2; q < p.tail_parts; ++q) {
+            const float4* src = tail_src + static_cast<size_t>(q - 1) * (tail_tile_elems / 4) + static_cast<size_t>(c) * 8u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 t = __ldcg(src + j * 32);
+              x[4 * j] += t.x;
+              x[4 * j + 1] += t.y;
+              x[4 * j + 2] += t.z;
+              x[4 * j + 3] += t.w;
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] *= alpha;
         if (p.bias != nullptr) {
           if (p.bias_axis == 0) {
 #pragma unroll
@@ -447,6 +611,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
         }
         if (row_ok) store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid);
+      }
+      if (w.part > 0 && exchange) {
+        // Publish: every lane's stores are ordered before the flag the owner polls.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          uint32_t* flag = p.tail_flags + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (w.part - 1)) * (CG * 4) + flag_lane;
+          st_release_gpu(flag, p.epoch);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -171,6 +171,13 @@ struct b200_gemm_plan {
   int num_kb = 0;     // per split
   int m_blocks = 0, n_blocks = 0;
   int raster_group = 8;
+  // Tail split (see gemm::Params): decided from the tile count and the persistent grid.
+  int units_cap = kDefaultSms;  // CTAs (pairs) the persistent grid may use
+  int tail_tiles = 0, tail_parts = 0, tail_kb0 = 0, tail_kb = 0;
+  int64_t tail_ws_bytes = 0;   // flags + partial tiles; 0 = tail split not useful for this plan
+  int64_t tail_flag_bytes = 0;
+  const void* tail_ws_seen = nullptr;  // workspace whose flag area has been zeroed
+  uint32_t epoch = 0;
   KernelFn kernel = nullptr;
   bool attr_set = false;
   int attr_device = -1;
@@ -189,6 +196,52 @@ bool direct_b(const b200_gemm_plan* p) { return p->desc.b_layout != B200_B_ROW_M
 int64_t packed_b_bytes(const b200_gemm_plan* p) {
   if (!direct_b(p)) return 0;
   return static_cast<int64_t>(p->n_blocks) * p->total_kb * p->bn * gemm::kRowBytes;
+}
+
+// Decide whether the last, partly filled round of tiles should be cut along K.  `units` =
+// CTAs (pairs) in the persistent grid.  Worth it when the last round would keep at most half
+// of the units busy and each K range still has a few K blocks.
+void plan_tail_split(b200_gemm_plan* plan) {
+  plan->tail_tiles = plan->tail_parts = plan->tail_kb0 = plan->tail_kb = 0;
+  plan->tail_ws_bytes = plan->tail_flag_bytes = 0;
+  if (plan->split_k > 1 || plan->desc.reserved[1] == 1) return;  // reserved[1] = 1: caller opted out
+  const int units = plan->units_cap;
+  const int tiles = plan->m_blocks * plan->n_blocks;
+  if (units < 2 || tiles < 1) return;
+  const int tail = tiles % units;  // tiles < units: every tile is a tail tile
+  if (tail == 0) return;
+  int parts = units / tail;
+  if (parts > 8) parts = 8;
+  if (parts < 2) return;
+  while (parts >= 2 && plan->num_kb / parts < 4) --parts;
+  if (parts < 2) return;
+  // The owner (part 0) takes a few more K blocks than the contributors, so that their partial
+  // tiles are already in the workspace when the owner's own MMAs finish.
+  int kb0 = (plan->num_kb + parts - 1) / parts + 5;
+  if (kb0 > plan->num_kb - (parts - 1)) kb0 = plan->num_kb - (parts - 1);
+  const int rest = plan->num_kb - kb0;
+  const int tail_kb = (rest + parts - 2) / (parts - 1);
+  parts = 1 + (rest + tail_kb - 1) / tail_kb;
+  if (parts < 2) return;
+  plan->tail_tiles = tail;
+  plan->tail_parts = parts;
+  plan->tail_kb0 = kb0;
+  plan->tail_kb = tail_kb;
+  const int64_t flags = static_cast<int64_t>(tail) * (parts - 1) * plan->cg * 4 * sizeof(uint32_t);
+  plan->tail_flag_bytes = (flags + 255) / 256 * 256;
+  plan->tail_ws_bytes = plan->tail_flag_bytes +
+                        static_cast<int64_t>(tail) * (parts - 1) * (gemm::kBM * plan->cg) * plan->bn * sizeof(float);
+}
+
+// Persistent grid: one CTA (pair) per work item up to `units_cap`.
+void size_grid(b200_gemm_plan* plan, int units_cap) {
+  plan->units_cap = units_cap < 1 ? 1 : units_cap;
+  plan_tail_split(plan);
+  const int64_t tiles = static_cast<int64_t>(plan->m_blocks) * plan->n_blocks;
+  int64_t items = plan->split_k > 1 ? tiles * plan->split_k : tiles;
+  if (plan->tail_parts > 1) items = tiles - plan->tail_tiles + static_cast<int64_t>(plan->tail_tiles) * plan->tail_parts;
+  const int64_t units = items < plan->units_cap ? items : plan->units_cap;
+  plan->grid = static_cast<int>(units) * plan->cg;
 }
 
 int64_t workspace_bytes(const b200_gemm_plan* p) {
@@ -210,8 +263,8 @@ int ensure_device_state(b200_gemm_plan* plan) {
     int sms = kDefaultSms;
     B200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     plan->sm_count = sms;
-    const int items = plan->m_blocks * plan->n_blocks * plan->split_k;
     int cap = plan->desc.max_ctas > 0 ? plan->desc.max_ctas : sms;
+    int units_cap = cap;
     if (plan->cg == 2) {
       // Persistent pairs: as many clusters of two as can be resident at once.
       cudaLaunchConfig_t cfg = {};
@@ -230,13 +283,11 @@ int ensure_device_state(b200_gemm_plan* plan) {
         cudaGetLastError();
         clusters = sms / 2;
       }
-      int pairs = cap / 2 < 1 ? 1 : cap / 2;
-      if (pairs > clusters) pairs = clusters;
-      if (pairs > items) pairs = items;
-      plan->grid = 2 * pairs;
-    } else {
-      plan->grid = items < cap ? items : cap;
+      units_cap = cap / 2 < 1 ? 1 : cap / 2;
+      if (units_cap > clusters) units_cap = clusters;
     }
+    size_grid(plan, units_cap);
+    plan->tail_ws_seen = nullptr;
     plan->attr_set = true;
     plan->attr_device = dev;
     plan->map_a_ptr = plan->map_b_ptr = nullptr;
@@ -268,7 +319,7 @@ int check_run_args(const b200_gemm_plan* plan, const void* A, const void* B, con
 }
 
 int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias, const float* scale_a,
-           const float* scale_b, void* workspace, cudaStream_t stream) {
+           const float* scale_b, void* workspace, size_t workspace_size, cudaStream_t stream) {
   const b200_gemm_desc& d = plan->desc;
   if (plan->map_a_ptr != A) {
     int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);  // per CTA
@@ -311,6 +362,23 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.workspace = static_cast<float*>(workspace);
   p.status = plan->status;
   p.debug_mode = d.reserved[0];
+  if (plan->tail_parts > 1 && workspace != nullptr && static_cast<int64_t>(workspace_size) >= plan->tail_ws_bytes &&
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
+    // The caller lent the optional workspace: cut the last round of tiles along K.
+    if (plan->tail_ws_seen != workspace) {
+      B200_CUDA_OK(cudaMemsetAsync(workspace, 0, static_cast<size_t>(plan->tail_flag_bytes), stream));
+      plan->tail_ws_seen = workspace;
+      plan->epoch = 0;
+    }
+    p.tail_tiles = plan->tail_tiles;
+    p.tail_parts = plan->tail_parts;
+    p.tail_kb0 = plan->tail_kb0;
+    p.tail_kb = plan->tail_kb;
+    p.tail_flags = static_cast<uint32_t*>(workspace);
+    p.tail_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + plan->tail_flag_bytes);
+    p.epoch = ++plan->epoch;
+    if (p.epoch == 0) p.epoch = ++plan->epoch;  // 0 is the cleared state of a flag
+  }
   if (plan->cg == 2) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(plan->grid));
@@ -444,14 +512,8 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   if (2 * gemm::tmem_columns(bn) > 512 && plan->smem <= kMaxSmemOptin / 2) plan->smem = kMaxSmemOptin / 2 + 1024;
   plan->raster_group = d.raster_group > 0 ? d.raster_group : 8;
   plan->kernel = select_kernel(bn, d.dtype_c, cg);
-  const int items = plan->m_blocks * plan->n_blocks * plan->split_k;
   const int cap = d.max_ctas > 0 ? d.max_ctas : kDefaultSms;
-  if (cg == 2) {
-    int pairs = cap / 2 < 1 ? 1 : cap / 2;
-    plan->grid = 2 * (items < pairs ? items : pairs);
-  } else {
-    plan->grid = items < cap ? items : cap;
-  }
+  size_grid(plan, cg == 2 ? (cap / 2 < 1 ? 1 : cap / 2) : cap);
   *out = plan;
   return B200_OK;
 }
@@ -481,6 +543,9 @@ int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* ou
   out->num_tiles = static_cast<int64_t>(plan->m_blocks) * plan->n_blocks;
   out->workspace_bytes = workspace_bytes(plan);
   out->packed_b_bytes = packed_b_bytes(plan);
+  out->optional_workspace_bytes = plan->tail_ws_bytes;
+  out->tail_tiles = plan->tail_tiles;
+  out->tail_parts = plan->tail_parts;
   // Registers per thread come from the loaded function; without a device this stays -1.
   out->regs_per_thread = -1;
   cudaFuncAttributes fa;
@@ -512,7 +577,7 @@ int b200_gemm_run(b200_gemm_plan* plan, const void* A, const void* B, void* C, c
   if (rc != B200_OK) return rc;
   rc = ensure_device_state(plan);
   if (rc != B200_OK) return rc;
-  return launch(plan, A, B, C, bias, scale_a, scale_b, workspace, b200::as_stream(stream));
+  return launch(plan, A, B, C, bias, scale_a, scale_b, workspace, workspace_bytes_in, b200::as_stream(stream));
 }
 
 int b200_gemm_time(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias, const float* scale_a,
@@ -530,7 +595,7 @@ int b200_gemm_time(b200_gemm_plan* plan, const void* A, const void* B, void* C, 
     if (flush_l2) rc = b200_flush_l2(nullptr);
     if (rc != B200_OK) break;
     cudaEventRecord(e0, nullptr);
-    rc = launch(plan, A, B, C, bias, scale_a, scale_b, workspace, nullptr);
+    rc = launch(plan, A, B, C, bias, scale_a, scale_b, workspace, workspace_bytes_in, nullptr);
     cudaEventRecord(e1, nullptr);
     cudaError_t e = cudaEventSynchronize(e1);
     if (rc == B200_OK && e != cudaSuccess) rc = b200::fail(B200_ERR_CUDA, "gemm_time: %s", cudaGetErrorString(e));
@@ -553,7 +618,7 @@ int b200_gemm_time_batch(b200_gemm_plan* plan, const void* A, const void* B, voi
   B200_CUDA_OK(cudaEventCreate(&e0));
   B200_CUDA_OK(cudaEventCreate(&e1));
   cudaEventRecord(e0, nullptr);
-  for (int it = 0; it < iters && rc == B200_OK; ++it) rc = launch(plan, A, B, C, bias, scale_a, scale_b, workspace, nullptr);
+  for (int it = 0; it < iters && rc == B200_OK; ++it) rc = launch(plan, A, B, C, bias, scale_a, scale_b, workspace, workspace_bytes_in, nullptr);
   cudaEventRecord(e1, nullptr);
   cudaError_t e = cudaEventSynchronize(e1);
   if (rc == B200_OK && e != cudaSuccess) rc = b200::fail(B200_ERR_CUDA, "gemm_time_batch: %s", cudaGetErrorString(e));

@@ -204,6 +204,7 @@ def gemm(
     shape: Optional[tuple] = None,
     plan: Optional[GemmPlan] = None,
     b_layout: str = "row_major",
+    tail_split: bool = False,
     **plan_kw,
 ) -> np.ndarray:
     """``C = epilogue(A . B^T)`` on the GPU with host arrays in and a host array out.
@@ -211,7 +212,9 @@ def gemm(
     A is ``[M, K]``, B is ``[N, K]`` (both K-contiguous), stored as float16, or as bf16 /
     e4m3 bit patterns (uint16 / uint8; see :mod:`aster_b200.dtypes`).  ``B`` in a direct-B
     layout ("ref_preshuffled" or "packed" = row-major to be packed) is packed on the device
-    first.  Returns ``[M, N]`` float32, or bf16 bit patterns (uint16) for ``dtype_c="bf16"``.
+    first.  ``tail_split=True`` lends the plan its optional workspace so that a mostly idle
+    last round of tiles is cut along K (changes the fp32 summation order of those tiles).
+    Returns ``[M, N]`` float32, or bf16 bit patterns (uint16) for ``dtype_c="bf16"``.
     """
     if shape is None:
         M, K = A.shape
@@ -249,8 +252,9 @@ def gemm(
         dC = GpuBuffer(out.nbytes)
         bufs.append(dC)
         ws = None
-        if res.workspace_bytes:
-            ws = GpuBuffer(res.workspace_bytes)
+        ws_bytes = res.workspace_bytes or (res.optional_workspace_bytes if tail_split else 0)
+        if ws_bytes:
+            ws = GpuBuffer(ws_bytes)
             bufs.append(ws)
         plan.run(dA, dB, dC, dbias, dsa, dsb, ws)
         plan.status()
@@ -319,7 +323,8 @@ class HostGemmPipeline:
         self.dA = [GpuBuffer(self.a_bytes) for _ in range(depth)]
         self.dB = [GpuBuffer(self.b_bytes) for _ in range(depth)]
         self.dC = [GpuBuffer(self.c_bytes) for _ in range(depth)]
-        self.ws = [GpuBuffer(res.workspace_bytes) if res.workspace_bytes else None for _ in range(depth)]
+        ws_bytes = res.workspace_bytes or res.optional_workspace_bytes
+        self.ws = [GpuBuffer(ws_bytes) if ws_bytes else None for _ in range(depth)]
         self.hC = [PinnedArray((plan.M, plan.N), STORAGE[plan.dtype_c]) for _ in range(depth)]
         self._small = []
         self.bias = self._upload_small(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None

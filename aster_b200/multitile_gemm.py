@@ -138,8 +138,9 @@ def execute_multitile_hsaco(cfg: B200GemmInstance, hsaco_path: str, num_iteratio
             bias_dev.copy_from_host(np.ascontiguousarray(bias, dtype=np.float32))
             extra.append(bias_dev)
         ws = None
-        if res.workspace_bytes:
-            ws = GpuBuffer(res.workspace_bytes)
+        ws_bytes = res.workspace_bytes or res.optional_workspace_bytes
+        if ws_bytes:
+            ws = GpuBuffer(ws_bytes)
             extra.append(ws)
 
         def launch(a_buf, b_buf, c_buf):

@@ -373,7 +373,8 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
             arr = np.atleast_1d(np.asarray(ops[key], dtype=np.float32))
             small[key] = GpuBuffer(arr.nbytes)
             small[key].copy_from_host(arr)
-    ws = GpuBuffer(res.workspace_bytes) if res.workspace_bytes else None
+    ws_bytes = res.workspace_bytes or res.optional_workspace_bytes
+    ws = GpuBuffer(ws_bytes) if ws_bytes else None
 
     def run_step(i):
         dA, dB, dC = sets[i % n_sets]
@@ -451,6 +452,7 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
             "workload": w["text"], "name": name, "per_gpu_shape": [rows, N, K], "global_rows": rows * world,
             "parallelism": f"m-row shards x{world}, B replicated, no collective",
             "tile": [res.tile_m, res.tile_n, res.tile_k], "stages": res.stages, "split_k": res.split_k, "grid_ctas": res.grid_ctas,
+            "cta_group": res.cta_group, "tail_split": [res.tail_tiles, res.tail_parts],
             "l2": f"rotating {n_sets} operand sets ({n_sets * set_bytes / 2**20:.0f} MiB) > {L2_BYTES / 1e6:.0f} MB L2",
         },
         "roofline": {

@@ -124,7 +124,7 @@ typedef struct b200_gemm_desc {
   int32_t split_k;   /* K partitions reduced through an fp32 workspace; 0/1 = none, -1 = choose */
   int32_t max_ctas;  /* persistent grid size cap; 0 = number of SMs                             */
   int32_t raster_group; /* m-blocks per rasterisation group; 0 = choose                         */
-  int32_t reserved[3];
+  int32_t reserved[3];  /* [0] kernel bring-up mode (0 = normal), [1] 1 = never use the tail split */
   char label[256];   /* provenance only: the reference label string (gemm_config.py:678-701)    */
 } b200_gemm_desc;
 
@@ -138,6 +138,13 @@ typedef struct b200_gemm_resources {
   int64_t num_tiles;
   int64_t workspace_bytes; /* required size of the run-time workspace (0 if none)               */
   int64_t packed_b_bytes;  /* size of the packed B buffer (0 for row-major plans)               */
+  /* Tail split: when the tile count leaves the last round of the persistent grid mostly idle,
+   * a caller that lends a 256-byte aligned workspace of at least optional_workspace_bytes lets
+   * the last tail_tiles tiles be cut into tail_parts K ranges on otherwise idle SMs (partials
+   * meet in the workspace, fixed summation order).  0 = not useful for this plan.  Without the
+   * workspace the plan runs whole tiles only. */
+  int64_t optional_workspace_bytes;
+  int32_t tail_tiles, tail_parts;
 } b200_gemm_resources;
 
 typedef struct b200_gemm_plan b200_gemm_plan;
@@ -159,7 +166,8 @@ int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, vo
  * plans.  C: [M,N] row-major, fully overwritten.  bias: fp32, length N (or M), may be NULL
  * when the epilogue has no bias.  scale_a / scale_b: device pointers to one fp32 each
  * (per-tensor dequantisation scales), NULL = 1.0.  workspace: device scratch of at least
- * resources.workspace_bytes (may be NULL when that is 0). */
+ * resources.workspace_bytes (may be NULL when that is 0); a workspace of at least
+ * resources.optional_workspace_bytes additionally enables the tail split. */
 int b200_gemm_run(b200_gemm_plan* plan, const void* A, const void* B, void* C,
                   const float* bias, const float* scale_a, const float* scale_b,
                   void* workspace, size_t workspace_bytes, void* stream);

@@ -42,7 +42,7 @@ def test_binding_covers_every_declared_symbol():
 def test_struct_sizes_match_header_layout(native_lib):
     # int64 x3 + int32 x16 + char[256]; int32 x12 + int64 x3; char[128] + int32 x10 + int64
     assert C.sizeof(nat.GemmDesc) == 24 + 64 + 256
-    assert C.sizeof(nat.GemmResources) == 48 + 24
+    assert C.sizeof(nat.GemmResources) == 48 + 24 + 16
     assert C.sizeof(nat.Props) == 128 + 40 + 8
 
 
@@ -99,7 +99,10 @@ def test_plan_resources_without_a_gpu(native_lib):
     p.destroy()
     p.destroy()  # idempotent
     small = GemmPlan(512, 512, 512).resources()
-    assert small.tile_n == 64 and small.num_tiles == 16 and small.cta_group == 2 and small.grid_ctas == 32
+    assert small.tile_n == 64 and small.num_tiles == 16 and small.cta_group == 2
+    assert (small.tail_tiles, small.tail_parts, small.grid_ctas) == (16, 2, 64) and small.optional_workspace_bytes > 0
+    assert (r.tail_tiles, r.tail_parts) == (34, 2) and r.optional_workspace_bytes == 34 * (256 * 256 * 4 + 32) + 0 * 256 or r.optional_workspace_bytes > 34 * 256 * 256 * 4
+    assert GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources().tail_parts == 0
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()
     assert fp8.tile_k == 128
     skinny = GemmPlan(16, 8192, 8192, "bf16", "bf16", split_k=-1, tile_n=64).resources()

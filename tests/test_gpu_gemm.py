@@ -237,6 +237,59 @@ class TestCtaPair:
             run(m, 192, 128, "bf16", "bf16", "uniform", m, cta_group=2, tile_n=64)
 
 
+class TestTailSplit:
+    """The last, partly filled round of tiles cut along K when the caller lends the workspace."""
+
+    @pytest.mark.parametrize("shape,kw", [
+        ((4096, 4096, 1024), {}),                                   # 256 tiles on 74 pairs: 34 tail tiles x 2 parts
+        ((1024, 1024, 2048), dict(tile_n=256)),                     # 16 tiles, all tail: 4 parts
+        ((512, 512, 512), {}),                                      # 16 small tiles x 2 parts
+        ((1280, 512, 4096), dict(tile_n=128, max_ctas=16)),         # 20 tiles on 8 pairs: 4 tail tiles x 2 parts
+        ((640, 512, 2048), dict(cta_group=1, tile_n=128, max_ctas=16)),  # single CTAs: 20 tiles on 16 CTAs -> 4 tail x 4 parts
+        ((300, 200, 1032), dict(tile_n=64)),                        # ragged edges in the exchanged tiles
+    ])
+    @pytest.mark.parametrize("dtype_c", ["f32", "bf16"])
+    def test_against_oracle(self, gpu, shape, kw, dtype_c):
+        M, N, K = shape
+        plan = GemmPlan(M, N, K, "bf16", dtype_c, **kw)
+        assert plan.resources().tail_parts >= 2, "case does not exercise the tail split"
+        run(M, N, K, "bf16", dtype_c, "uniform", 1, tail_split=True, **kw)
+
+    def test_epilogue_and_fp8(self, gpu):
+        run(1024, 1024, 2048, "bf16", "bf16", "normal", 2, bias=True, relu=True, tail_split=True, tile_n=256)
+        run(1024, 1024, 4096, "e4m3", "bf16", "normal", 3, tail_split=True, tile_n=256)
+
+    def test_repeated_launches_reuse_the_workspace(self, gpu):
+        from aster_b200.execution import GpuBuffer
+
+        M = N = 1024
+        K = 2048
+        inp = orc.make_inputs(M, N, K, "bf16", "uniform", 7)
+        plan = GemmPlan(M, N, K, "bf16", "f32", tile_n=256)
+        res = plan.resources()
+        dA, dB, dC = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes), GpuBuffer(M * N * 4)
+        dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
+        ws = GpuBuffer(res.optional_workspace_bytes)
+        outs = []
+        for _ in range(4):
+            dC.zero()
+            plan.run(dA, dB, dC, workspace=ws)
+            plan.status()
+            out = np.empty((M, N), np.float32)
+            dC.copy_to_host(out)
+            outs.append(out)
+        assert all(np.array_equal(outs[0], o) for o in outs[1:])  # fixed summation order
+        assert float(np.max(np.abs(outs[0] - orc.gemm_f32(inp["A"], inp["B"], "bf16")))) <= orc.abs_bound(inp["A"], inp["B"], "bf16")
+        # without the workspace the same plan computes whole tiles
+        plan.run(dA, dB, dC)
+        plan.status()
+        whole = np.empty((M, N), np.float32)
+        dC.copy_to_host(whole)
+        assert np.allclose(whole, outs[0], rtol=1e-5, atol=1e-3)
+        for b in (dA, dB, dC, ws):
+            b.free()
+
+
 class TestEpilogue:
     @pytest.mark.parametrize("dtype_c", ["f32", "bf16"])
     @pytest.mark.parametrize("bias,relu", [(True, True), (True, False), (False, True)])
