@@ -133,40 +133,32 @@ int launch_elementwise(const typename Op::T* a, const typename Op::T* b, typenam
 
 // dst[r, c] = src[r, c] for r < M, c < N; both row-major with pitch N, N % 4 == 0.
 //
-// Work item = (row, column tile of kThreads*4 columns): the reference's (row, 256-column tile)
-// per 64-lane wave (examples/06_copy_layout/copy_2d_padded.py:46-55) widened to a 256-thread
-// CTA.  Items are dealt to the persistent CTAs in groups of DEPTH consecutive items, group g
-// to CTA g % num_ctas (the reference deals single items the same way, :74-76), and all DEPTH
-// loads of a group are issued before its first store, which is the reference's `depth`
-// software pipelining (:71-96).  A lane whose column is >= N neither loads nor stores: the
-// per-dimension out-of-bounds rule the reference gets from buffer descriptors.
+// The reference tiles the M x N iteration space into (row, 256-column tile) items, pads the
+// last column tile and relies on buffer descriptors to drop the lanes that fall outside
+// (examples/06_copy_layout/copy_2d_padded.py:46-69).  With rows packed back to back and N a
+// multiple of 4, the matrix is one run of M*N/4 16-byte vectors, none of which straddles a row
+// or leaves the matrix, so this kernel walks that run directly: no padded lanes, no per-item
+// division, and the tail of one row coalesces with the head of the next.  Elements outside
+// M x N are never addressed, which is the contract the reference's sentinel check tests.
+// DEPTH = 16-byte loads each thread has in flight before its first store: the reference's
+// `depth` software-pipelining knob (:71-96).  Chunks of kThreads * DEPTH vectors are dealt
+// round-robin to the persistent CTAs, like the reference deals items (:74-76).
 template <int DEPTH>
-__global__ void __launch_bounds__(kThreads) copy_2d_padded_kernel(const float* __restrict__ src,
-                                                                 float* __restrict__ dst, long long M, long long N,
-                                                                 unsigned n_col_tiles, unsigned long long n_items) {
-  constexpr int kTileN = kThreads * 4;
-  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * DEPTH;
-  for (unsigned long long first = static_cast<unsigned long long>(blockIdx.x) * DEPTH; first < n_items; first += stride) {
+__global__ void __launch_bounds__(kThreads) copy_2d_padded_kernel(const float4* __restrict__ src, float4* __restrict__ dst,
+                                                                 size_t nvec) {
+  const size_t chunk = static_cast<size_t>(kThreads) * DEPTH;
+  const size_t nchunks = nvec / chunk;
+  for (size_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
+    const size_t base = ch * chunk + threadIdx.x;
     float4 v[DEPTH];
-    long long off[DEPTH];
 #pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      const unsigned long long item = first + d;
-      off[d] = -1;
-      if (item < n_items) {
-        const unsigned long long row = item / n_col_tiles;
-        const unsigned ct = static_cast<unsigned>(item - row * n_col_tiles);
-        const long long col = static_cast<long long>(ct) * kTileN + threadIdx.x * 4;
-        if (col < N) off[d] = static_cast<long long>(row) * N + col;
-      }
-    }
+    for (int d = 0; d < DEPTH; ++d) v[d] = ld_stream(src + base + d * kThreads);
 #pragma unroll
-    for (int d = 0; d < DEPTH; ++d)
-      if (off[d] >= 0) v[d] = ld_stream(reinterpret_cast<const float4*>(src + off[d]));
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d)
-      if (off[d] >= 0) st_stream(reinterpret_cast<float4*>(dst + off[d]), v[d]);
+    for (int d = 0; d < DEPTH; ++d) st_stream(dst + base + d * kThreads, v[d]);
   }
+  const size_t gsz = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = nchunks * chunk + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += gsz)
+    st_stream(dst + i, ld_stream(src + i));
 }
 
 }  // namespace
@@ -195,24 +187,22 @@ int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, 
   if (M == 0 || N == 0) return B200_OK;
   B200_REQUIRE(src && dst, "copy_2d_padded: NULL pointer");
   B200_REQUIRE(aligned16(src) && aligned16(dst), "copy_2d_padded: pointers must be 16-byte aligned");
-  constexpr int kTileN = kThreads * 4;
-  const unsigned long long n_col_tiles = (static_cast<unsigned long long>(N) + kTileN - 1) / kTileN;
-  B200_REQUIRE(n_col_tiles < (1ull << 32), "copy_2d_padded: N too large");
-  const unsigned long long n_items = static_cast<unsigned long long>(M) * n_col_tiles;
+  const size_t nvec = static_cast<size_t>(M) * static_cast<size_t>(N) / 4;
   // Round depth up to the instantiated pipeline depths {1,2,4,8}.
   int d = 1;
   while (d < depth) d *= 2;
-  unsigned long long want = (n_items + d - 1) / d;
-  unsigned long long cap = num_ctas > 0 ? static_cast<unsigned long long>(num_ctas)
-                                        : static_cast<unsigned long long>(sm_count()) * kCtasPerSm;
+  const size_t per_cta = static_cast<size_t>(kThreads) * d;
+  const size_t want = (nvec + per_cta - 1) / per_cta;
+  const size_t cap = num_ctas > 0 ? static_cast<size_t>(num_ctas) : static_cast<size_t>(sm_count()) * kCtasPerSm;
   const int grid = static_cast<int>(want < cap ? want : cap);
   cudaStream_t s = b200::as_stream(stream);
-  const unsigned nct = static_cast<unsigned>(n_col_tiles);
+  const float4* s4 = reinterpret_cast<const float4*>(src);
+  float4* d4 = reinterpret_cast<float4*>(dst);
   switch (d) {
-    case 1: copy_2d_padded_kernel<1><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
-    case 2: copy_2d_padded_kernel<2><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
-    case 4: copy_2d_padded_kernel<4><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
-    default: copy_2d_padded_kernel<8><<<grid, kThreads, 0, s>>>(src, dst, M, N, nct, n_items); break;
+    case 1: copy_2d_padded_kernel<1><<<grid, kThreads, 0, s>>>(s4, d4, nvec); break;
+    case 2: copy_2d_padded_kernel<2><<<grid, kThreads, 0, s>>>(s4, d4, nvec); break;
+    case 4: copy_2d_padded_kernel<4><<<grid, kThreads, 0, s>>>(s4, d4, nvec); break;
+    default: copy_2d_padded_kernel<8><<<grid, kThreads, 0, s>>>(s4, d4, nvec); break;
   }
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());

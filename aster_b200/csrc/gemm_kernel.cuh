@@ -515,7 +515,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const size_t tail_tile_elems = static_cast<size_t>(kTileM) * BN;
       const int flag_lane = (static_cast<int>(cta_rank) * 4 + quarter);
       const size_t warp_slab = static_cast<size_t>(flag_lane) * (32u * BN);  // floats per warp = 32 rows x BN
-      const bool exchange = (p.debug_mode & 4) == 0;
+      // A warp whose 32 rows all lie beyond M has nothing to read, exchange or store.
+      const bool slab_ok = (m_blk * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32) < p.M;
+      const bool exchange = (p.debug_mode & 4) == 0 && slab_ok;
       if (w.part == 0 && exchange) {
         // Owner: the contributors' partial sums for these 32 rows must have landed.
         for (int q = 1; q < p.tail_parts; ++q) {
@@ -536,7 +538,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + j * 32);
       }
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < (slab_ok ? BN : 0); c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(c), v);
         tmem_ld_wait();

@@ -51,9 +51,9 @@ WORKLOADS = {
                      text="fp8-e4m3 GEMM M=N=K=8192, per-tensor scales amax/448, N(0,1) seed 3, bf16 out"),
     "sharded_65536": dict(M=65536, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, strong=True,
                           text="bf16 GEMM M=65536 N=K=8192 split by M rows over the GPUs, U(-1,1) seed 4"),
-    "decode_16": dict(M=16, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, split_k=-1, tile_n=64, hbm=True,
+    "decode_16": dict(M=16, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True,
                       text="bf16 skinny GEMM M=16 N=K=8192, U(-1,1) seed 4"),
-    "decode_128": dict(M=128, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, split_k=-1, tile_n=64, hbm=True,
+    "decode_128": dict(M=128, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True,
                        text="bf16 skinny GEMM M=128 N=K=8192, U(-1,1) seed 4"),
     "vector_add": dict(n=1 << 28, text="int32 vector_add, 2^28 elements per array, integers from default_rng(5)"),
     "vector_add_64m": dict(n=1 << 26, text="int32 vector_add, 2^26 elements per array (profiling size), integers from default_rng(5)"),
