@@ -87,7 +87,9 @@ struct Params {
   float* tail_ws;         // [tail_tiles][tail_parts - 1][tile rows][BN] fp32
   uint32_t* tail_flags;   // [tail_tiles][tail_parts - 1][CG][4 epilogue warps]
   uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
-  int debug_mode;  // 0 = normal; 1 = producer signals without copying; 2 = MMA warp commits without multiplying
+  int debug_mode;  // bits 0-1: 1 = producer signals without copying, 2 = MMA warp commits without multiplying;
+                   // bit 2: skip the tail-split exchange; bit 3: producer never signals (exercises the wait limit)
+  unsigned wait_limit_ms;  // limit of every bounded wait; 0 = default
 };
 
 __host__ __device__ constexpr int stage_bytes(int bn, int cg = 1) { return (kBM + bn / cg) * kRowBytes; }
@@ -102,24 +104,25 @@ __host__ __device__ constexpr int tmem_columns(int bn) { return 2 * bn < 32 ? 32
 struct Waiter {
   volatile uint32_t* abort_flag;
   uint32_t* status;
+  unsigned long long limit_ns;
 
   // Wait for an mbarrier phase with a time limit.  Returns false when the CTA is aborting.
   // The first poll is inline; only a miss pays for the bookkeeping of the bounded spin.
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code, int tile, int kb,
-                                       unsigned long long limit_ns = kWaitTimeoutNs) const {
+                                       unsigned long long limit = 0) const {
     if (sm100::mbar_try_wait(bar, parity)) return true;
-    return wait_slow(bar, parity, code, tile, kb, limit_ns);
+    return wait_slow(bar, parity, code, tile, kb, limit != 0 ? limit : limit_ns);
   }
 
   __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, uint32_t code, int tile, int kb,
-                                         unsigned long long limit_ns) const {
+                                         unsigned long long limit) const {
     const unsigned long long t0 = sm100::globaltimer_ns();
 #pragma unroll 1
     for (uint32_t spin = 1;; ++spin) {
       if (sm100::mbar_try_wait(bar, parity)) return true;
       if ((spin & 63u) == 0u) {
         if (*abort_flag != 0u) return false;
-        if (sm100::globaltimer_ns() - t0 > limit_ns) {
+        if (sm100::globaltimer_ns() - t0 > limit) {
           if (code != 0u && atomicCAS(status, 0u, code) == 0u) {
             status[1] = blockIdx.x;
             status[2] = static_cast<uint32_t>(tile);
@@ -149,7 +152,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, c
           ok = 0;
           break;
         }
-        if (sm100::globaltimer_ns() - t0 > kWaitTimeoutNs) {
+        if (sm100::globaltimer_ns() - t0 > waiter.limit_ns) {
           if (atomicCAS(waiter.status, 0u, static_cast<uint32_t>(kStatusTailFlagWait)) == 0u) {
             waiter.status[1] = blockIdx.x;
             waiter.status[2] = static_cast<uint32_t>(tile);
@@ -318,7 +321,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     t_cycles = clock64();
     t_ns = globaltimer_ns();
   }
-  const Waiter waiter{abort_flag, p.status};
+  const Waiter waiter{abort_flag, p.status, p.wait_limit_ms != 0 ? p.wait_limit_ms * 1000000ull : kWaitTimeoutNs};
   const int num_items = num_work_items(p);
   const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;  // position in the pair
   const bool leader = cta_rank == 0u;
@@ -372,7 +375,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const int k_elem = (kb0 + kb) * p.kb_elems;
-          if ((p.debug_mode & 3) == 1) {
+          if (p.debug_mode & 8) {
+            // injected fault: the stage is never handed over, so the consumer's wait must run out
+          } else if ((p.debug_mode & 3) == 1) {
             if (leader) mbar_arrive(full_bar(stage));
           } else if constexpr (CG == 1) {
             mbar_arrive_expect_tx(full_bar(stage), kStageBytes);

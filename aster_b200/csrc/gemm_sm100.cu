@@ -362,6 +362,7 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.workspace = static_cast<float*>(workspace);
   p.status = plan->status;
   p.debug_mode = d.reserved[0];
+  p.wait_limit_ms = d.reserved[2] > 0 ? static_cast<unsigned>(d.reserved[2]) : 0u;
   if (plan->tail_parts > 1 && workspace != nullptr && static_cast<int64_t>(workspace_size) >= plan->tail_ws_bytes &&
       (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
     // The caller lent the optional workspace: cut the last round of tiles along K.

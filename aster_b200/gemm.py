@@ -61,6 +61,8 @@ class GemmPlan:
         raster_group: int = 0,
         label: str = "",
         debug_mode: int = 0,
+        no_tail_split: bool = False,
+        wait_limit_ms: int = 0,
     ) -> None:
         self._handle = None
         desc = nat.GemmDesc()
@@ -77,6 +79,8 @@ class GemmPlan:
         desc.stages, desc.cta_group, desc.split_k = stages, cta_group, split_k
         desc.max_ctas, desc.raster_group = max_ctas, raster_group
         desc.reserved[0] = debug_mode  # kernel bring-up aid: 1 = no copies, 2 = no multiplies (results are garbage)
+        desc.reserved[1] = 1 if no_tail_split else 0
+        desc.reserved[2] = wait_limit_ms
         desc.label = label.encode()[:255]
         handle = C.c_void_p()
         nat.call("b200_gemm_plan_create", C.byref(desc), C.byref(handle))

@@ -508,7 +508,7 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
     KERNEL_NAME = "gemm_multitile"
 
     def __init__(self, spec: GemmSpec, mapping: GemmMappingSpec, *, dtype_ab: str = "f16", dtype_c: str = "f32",
-                 epilogue: str = "none", bias_axis: str = "n", tile_n: int = 0, stages: int = 0, split_k: int = 0,
+                 epilogue: str = "none", bias_axis: str = "n", tile_n: int = 0, stages: Optional[int] = None, split_k: int = 0,
                  cta_group: int = 0):
         super().__init__(spec, mapping)
         if dtype_ab not in ("f16", "bf16", "e4m3") or dtype_c not in ("f32", "bf16"):
@@ -521,7 +521,8 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
             raise ValueError(f"spec output width {spec.elt_bytes_c} does not match dtype {dtype_c}")
         self.dtype_ab, self.dtype_c = dtype_ab, dtype_c
         self.epilogue, self.bias_axis = epilogue, bias_axis
-        self.tile_n_override, self.stages_override = int(tile_n), int(stages)
+        self.tile_n_override = int(tile_n)
+        self.stages_override = None if stages is None else int(stages)  # None: from the pipeline strategy; 0: as many as fit
         self.split_k, self.cta_group = int(split_k), int(cta_group)
 
     @property
@@ -561,8 +562,10 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
 
     @property
     def stages(self) -> int:
-        """Shared-memory ring depth: the override, else the pipeline strategy's depth."""
-        return self.stages_override or self.mapping.pipeline_depth
+        """Shared-memory ring depth handed to the plan: the ``_st`` override when the label has
+        one (``_st0`` = as many slots as fit in shared memory), else the pipeline strategy's
+        depth ``max(stage) + 1``."""
+        return self.mapping.pipeline_depth if self.stages_override is None else self.stages_override
 
     def plan_kwargs(self) -> dict:
         """Arguments for :class:`aster_b200.gemm.GemmPlan`."""
@@ -581,7 +584,7 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
             s += "_bm"
         if self.tile_n_override:
             s += f"_bn{self.tile_n_override}"
-        if self.stages_override:
+        if self.stages_override is not None:
             s += f"_st{self.stages_override}"
         if self.split_k:
             s += f"_sk{self.split_k}"
@@ -592,7 +595,7 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
     @property
     def is_plain(self) -> bool:
         return (self.dtype_ab, self.dtype_c, self.epilogue, self.bias_axis) == ("f16", "f32", "none", "n") and not (
-            self.tile_n_override or self.stages_override or self.split_k or self.cta_group
+            self.tile_n_override or self.stages_override is not None or self.split_k or self.cta_group
         )
 
     @property
@@ -610,7 +613,7 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
             base = label[: sm.start()]
             dt_ab, dt_c, epi, bm, bn, st, sk, cg = sm.groups()
             extras = dict(dtype_ab=dt_ab, dtype_c=dt_c, epilogue=_EPI_FROM_TOKEN[epi], bias_axis="m" if bm else "n",
-                          tile_n=int(bn or 0), stages=int(st or 0), split_k=int(sk or 0), cta_group=int(cg or 0))
+                          tile_n=int(bn or 0), stages=None if st is None else int(st), split_k=int(sk or 0), cta_group=int(cg or 0))
         spec, mapping = cls._parts_from_label(base)
         if extras:
             m, n, k = spec.gemm_size
@@ -623,11 +626,13 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
 
 
 def make_b200_instance(M: int, N: int, K: int, *, dtype_ab: str = "f16", dtype_c: str = "f32", epilogue: str = "none",
-                       bias_axis: str = "n", tile_n: int = 256, stages: int = 0, split_k: int = 0, cta_group: int = 0,
+                       bias_axis: str = "n", tile_n: int = 256, stages: Optional[int] = 0, split_k: int = 0, cta_group: int = 0,
                        operand_path: OperandPath = OperandPath.LDS, pipeline_strategy: int = 3) -> B200GemmInstance:
     """Build an instance for sizes that are multiples of 16, picking a workgroup grid whose
     tile is ``128 x tile_n`` when the sizes allow it (otherwise one workgroup spans the
-    dimension), with the reference's usual 1x4 wave grid."""
+    dimension), with the reference's usual 1x4 wave grid.  ``stages=0`` (default) lets the plan
+    use as many ring slots as fit; ``stages=None`` derives the depth from the pipeline strategy
+    and, with the other defaults, yields a plain reference label."""
     if M % 16 or N % 16:
         raise ValueError("the weak-scale identity needs M and N to be multiples of 16")
 

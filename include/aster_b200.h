@@ -124,7 +124,9 @@ typedef struct b200_gemm_desc {
   int32_t split_k;   /* K partitions reduced through an fp32 workspace; 0/1 = none, -1 = choose */
   int32_t max_ctas;  /* persistent grid size cap; 0 = number of SMs                             */
   int32_t raster_group; /* m-blocks per rasterisation group; 0 = choose                         */
-  int32_t reserved[3];  /* [0] kernel bring-up mode (0 = normal), [1] 1 = never use the tail split */
+  int32_t reserved[3];  /* [0] kernel bring-up mode (0 = normal; 8 = the producer never hands a stage
+                         * over, which makes the consumer's bounded wait expire), [1] 1 = never use
+                         * the tail split, [2] limit of the device-side waits in ms (0 = 2000) */
   char label[256];   /* provenance only: the reference label string (gemm_config.py:678-701)    */
 } b200_gemm_desc;
 

@@ -128,7 +128,7 @@ def test_peak_table_is_a_superset(golden):
 
 class TestB200Instance:
     def test_plain_label_is_reference_label(self):
-        cfg = make_b200_instance(4096, 4096, 4096)
+        cfg = make_b200_instance(4096, 4096, 4096, stages=None)
         assert "_b200_" not in cfg.label
         assert WeakScaledMappedGemmInstance.from_label(cfg.label).label == cfg.label
         assert cfg.tile_n == 256 and cfg.stages == 3 and cfg.requested_cta_tile == [128, 256, 32]
@@ -139,6 +139,8 @@ class TestB200Instance:
         dict(dtype_ab="bf16", dtype_c="bf16", epilogue="bias_relu"),
         dict(dtype_ab="bf16", dtype_c="bf16", epilogue="bias", bias_axis="m"),
         dict(dtype_ab="f16", dtype_c="f32", stages=4, split_k=-1),
+        dict(dtype_ab="f16", dtype_c="f32", stages=None),
+        dict(dtype_ab="f16", dtype_c="f32", stages=0),
         dict(dtype_ab="bf16", dtype_c="f32", epilogue="relu", tile_n=64, split_k=8, cta_group=1),
     ])
     def test_suffix_roundtrip(self, kw):
@@ -146,6 +148,12 @@ class TestB200Instance:
         back = B200GemmInstance.from_label(cfg.label)
         assert back.label == cfg.label
         assert back.plan_kwargs() == cfg.plan_kwargs()
+
+    def test_ring_depth_mapping(self):
+        assert make_b200_instance(256, 256, 256, stages=None, pipeline_strategy=9).stages == 6  # max(stage) + 1
+        auto = make_b200_instance(256, 256, 256)
+        assert auto.stages == 0 and auto.label.endswith("_st0") and auto.plan_kwargs()["stages"] == 0
+        assert make_b200_instance(256, 256, 256, stages=5).label.endswith("_st5")
 
     def test_tile_snapping(self):
         # twg_n * 16 = 32 -> 32; 112 -> 64; 400 -> 256

@@ -398,6 +398,43 @@ class TestProperties:
         assert np.array_equal(gemm(a, eye, dtype_ab="bf16", dtype_c="bf16"), a)
 
 
+class TestBoundedWaits:
+    """Failure detection without faulting the GPU: a wait that nothing will ever satisfy runs
+    into its time limit, the kernel records which wait gave up and returns normally, the host
+    reads B200_ERR_TIMEOUT, and the context (and the plan) stay usable."""
+
+    @pytest.mark.parametrize("cta_group", [1, 2])
+    def test_expired_wait_is_reported_not_hung(self, gpu, cta_group):
+        import time
+
+        from aster_b200 import _native as nat
+        from aster_b200.execution import GpuBuffer
+
+        M, N, K = 512, 256, 512
+        inp = orc.make_inputs(M, N, K, "bf16", "uniform", 3)
+        dA, dB, dC = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes), GpuBuffer(M * N * 4)
+        dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
+        stuck = GemmPlan(M, N, K, "bf16", "f32", cta_group=cta_group, tile_n=128, debug_mode=8, wait_limit_ms=50)
+        t0 = time.perf_counter()
+        stuck.run(dA, dB, dC)
+        with pytest.raises(nat.B200Error) as e:
+            stuck.status()
+        elapsed = time.perf_counter() - t0
+        # whichever role's wait expired first is named: 0x10 producer, 0x20 MMA issuer, 0x30 epilogue
+        assert e.value.status == nat.ERR_TIMEOUT and any(f"code 0x{c:x}" in e.value.message for c in (0x10, 0x20, 0x30))
+        assert 0.04 < elapsed < 2.0
+        assert stuck.status() == [0, 0, 0, 0]  # reading clears the words
+        # The device and the library are still healthy: the same operands through a normal plan.
+        good = GemmPlan(M, N, K, "bf16", "f32", cta_group=cta_group, tile_n=128)
+        good.run(dA, dB, dC)
+        good.status()
+        out = np.empty((M, N), np.float32)
+        dC.copy_to_host(out)
+        assert float(np.max(np.abs(out - orc.gemm_f32(inp["A"], inp["B"], "bf16")))) <= orc.abs_bound(inp["A"], inp["B"], "bf16")
+        for b in (dA, dB, dC):
+            b.free()
+
+
 class TestPlanObject:
     def test_timing_loops_and_status(self, gpu):
         from aster_b200.execution import GpuBuffer
