@@ -101,6 +101,21 @@ __host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1) {
 }
 __host__ __device__ constexpr int tmem_columns(int bn) { return 2 * bn < 32 ? 32 : 2 * bn; }  // bn is a power of two
 
+// Has more than `limit` ns passed since `t0`?  A single reading of the global timer is not
+// trusted: a reading that looks like an expiry is confirmed by a second one, and a start stamp
+// that lies in the future (a torn or stepped timer value) is replaced, so that one bad reading
+// cannot turn into a spurious timeout.
+__device__ __forceinline__ bool wait_expired(unsigned long long& t0, unsigned long long limit) {
+  const unsigned long long now = sm100::globaltimer_ns();
+  if (now < t0) {
+    t0 = now;
+    return false;
+  }
+  if (now - t0 <= limit) return false;
+  const unsigned long long again = sm100::globaltimer_ns();
+  return again >= now && again - t0 > limit;
+}
+
 struct Waiter {
   volatile uint32_t* abort_flag;
   uint32_t* status;
@@ -114,15 +129,48 @@ struct Waiter {
     return wait_slow(bar, parity, code, tile, kb, limit != 0 ? limit : limit_ns);
   }
 
+  // Wait of a whole warp that can afford some wake-up latency (the epilogue, which has a whole
+  // main loop of slack): lane 0 polls with a sleep between polls, the other lanes idle at the
+  // shuffle.  128 threads spinning on a barrier for the length of a main loop burn power that
+  // the tensor pipe could use -- the kernel runs against the board's power limit.
+  __device__ __forceinline__ bool wait_relaxed(uint32_t bar, uint32_t parity, uint32_t code, int tile, unsigned sleep_ns) const {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0 && !sm100::mbar_try_wait(bar, parity)) {
+      unsigned long long t0 = sm100::globaltimer_ns();
+#pragma unroll 1
+      for (uint32_t spin = 1;; ++spin) {
+        __nanosleep(sleep_ns);
+        if (sm100::mbar_try_wait(bar, parity)) break;
+        if ((spin & 15u) == 0u) {
+          if (*abort_flag != 0u) {
+            ok = 0;
+            break;
+          }
+          if (wait_expired(t0, limit_ns)) {
+            if (atomicCAS(status, 0u, code) == 0u) {
+              status[1] = blockIdx.x;
+              status[2] = static_cast<uint32_t>(tile);
+              status[3] = 0u;
+            }
+            *abort_flag = 1u;
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  }
+
   __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, uint32_t code, int tile, int kb,
                                          unsigned long long limit) const {
-    const unsigned long long t0 = sm100::globaltimer_ns();
+    unsigned long long t0 = sm100::globaltimer_ns();
 #pragma unroll 1
     for (uint32_t spin = 1;; ++spin) {
       if (sm100::mbar_try_wait(bar, parity)) return true;
       if ((spin & 63u) == 0u) {
         if (*abort_flag != 0u) return false;
-        if (sm100::globaltimer_ns() - t0 > limit) {
+        if (wait_expired(t0, limit)) {
           if (code != 0u && atomicCAS(status, 0u, code) == 0u) {
             status[1] = blockIdx.x;
             status[2] = static_cast<uint32_t>(tile);
@@ -142,7 +190,7 @@ struct Waiter {
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, const Waiter& waiter, int tile) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0 && sm100::ld_acquire_gpu(flag) != want) {
-    const unsigned long long t0 = sm100::globaltimer_ns();
+    unsigned long long t0 = sm100::globaltimer_ns();
 #pragma unroll 1
     for (uint32_t spin = 1;; ++spin) {
       __nanosleep(64);
@@ -152,7 +200,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, c
           ok = 0;
           break;
         }
-        if (sm100::globaltimer_ns() - t0 > waiter.limit_ns) {
+        if (wait_expired(t0, waiter.limit_ns)) {
           if (atomicCAS(waiter.status, 0u, static_cast<uint32_t>(kStatusTailFlagWait)) == 0u) {
             waiter.status[1] = blockIdx.x;
             waiter.status[2] = static_cast<uint32_t>(tile);
@@ -503,7 +551,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int split = w.split;
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
-      if (!waiter.wait(acc_full_bar(acc), acc_phase, kStatusEpilogueAccFullWait, tile, 0)) {
+      if (!waiter.wait_relaxed(acc_full_bar(acc), acc_phase, kStatusEpilogueAccFullWait, tile, 256u)) {
         ok = false;
         break;
       }
