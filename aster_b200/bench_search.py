@@ -257,7 +257,10 @@ def main(argv=None) -> int:
         return 0
     stream = open(args.results_file, "a") if args.results_file else sys.stdout
     try:
-        ranked = run_sweep(instances, iterations=args.iterations, results_stream=stream, verify_top=args.verify_top)
+        # fp8 results get their own registry slot: the size key alone would make them compete
+        # with the 16-bit configs of the same shape
+        bench = BENCH_HOOKS["bench_label"] + ("_fp8" if args.dtype == "e4m3" else "")
+        ranked = run_sweep(instances, iterations=args.iterations, results_stream=stream, verify_top=args.verify_top, bench=bench)
     finally:
         if args.results_file:
             stream.close()
