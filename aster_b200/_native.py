@@ -199,6 +199,17 @@ def call(name: str, *args) -> None:
     check(getattr(lib(), name)(*args))
 
 
+def init_current() -> int:
+    """Initialise the runtime on the device that is current for this thread (device 0 when
+    none has been chosen yet) and return its index.  Host-buffer helpers call this instead of
+    selecting a device themselves, so that a rank that picked its GPU keeps it."""
+    d = C.c_int(0)
+    if lib().b200_get_device(C.byref(d)) != OK:
+        d.value = 0
+    call("b200_init", d.value)
+    return d.value
+
+
 def launch_count() -> int:
     n = C.c_int64(0)
     call("b200_launch_count", C.byref(n))

@@ -40,7 +40,7 @@ def _elementwise(fn_name: str, a: np.ndarray, b: np.ndarray, dtype) -> np.ndarra
     out = np.empty_like(a)
     if a.size == 0:
         return out
-    nat.call("b200_init", 0)
+    nat.init_current()
     da, db, dc = GpuBuffer(a.nbytes), GpuBuffer(a.nbytes), GpuBuffer(a.nbytes)
     try:
         da.copy_from_host(a)
@@ -86,7 +86,7 @@ def copy_2d_padded(src: np.ndarray, dst: np.ndarray | None = None, *, depth: int
         raise ValueError(f"N={n} must be a multiple of 4 (a 16-byte access must not straddle a row)")
     if src.size == 0:
         return dst
-    nat.call("b200_init", 0)
+    nat.init_current()
     ds, dd = GpuBuffer(src.nbytes), GpuBuffer(dst.nbytes)
     try:
         ds.copy_from_host(src)

@@ -290,7 +290,10 @@ def execute_launch(
     argument per entry of ``arguments``: the :class:`GpuBuffer` for array wrappers, the value
     itself for scalars.  Returns the per-iteration times in nanoseconds.
     """
-    nat.call("b200_init", 0 if device_id is None else device_id)
+    if device_id is None:
+        nat.init_current()  # keep the caller's device, as the reference does
+    else:
+        nat.call("b200_init", device_id)
     nat.call("b200_clear_last_error")
     arguments = [InOutArray(a) if isinstance(a, np.ndarray) else a for a in arguments]
     owns_mm = memory_manager is None

@@ -233,7 +233,7 @@ def gemm(
         ]
         plan = GemmPlan(M, N, K, dtype_ab, dtype_c, b_layout=b_layout, epilogue=epilogue, bias_axis=bias_axis, **plan_kw)
     res = plan.resources()
-    nat.call("b200_init", 0)
+    nat.init_current()
     bufs = []
 
     def dev(arr: np.ndarray) -> GpuBuffer:
@@ -322,7 +322,7 @@ class HostGemmPipeline:
         eb_c = np.dtype(STORAGE[plan.dtype_c]).itemsize
         self.a_bytes, self.b_bytes = plan.M * plan.K * eb_ab, plan.N * plan.K * eb_ab
         self.c_bytes = plan.M * plan.N * eb_c
-        nat.call("b200_init", _current_device())
+        nat.init_current()
         self.streams = [GpuStream() for _ in range(depth)]
         self.dA = [GpuBuffer(self.a_bytes) for _ in range(depth)]
         self.dB = [GpuBuffer(self.b_bytes) for _ in range(depth)]

@@ -111,7 +111,7 @@ def execute_multitile_hsaco(cfg: B200GemmInstance, hsaco_path: str, num_iteratio
     if A.dtype != want or B.dtype != want:
         raise TypeError(f"A/B must be stored as {np.dtype(want)} for {cfg.dtype_ab}, got {A.dtype}/{B.dtype}")
     C_output = np.zeros(math.prod(cfg.spec.operand_shape(Operand.C)), dtype=STORAGE[cfg.dtype_c])
-    nat.call("b200_init", 0)
+    nat.init_current()
     extra = []
     try:
         if cfg.mapping.direct_b:

@@ -199,13 +199,25 @@ class Job:
         self.rank = int(os.environ.get("RANK", "0"))
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         self.dist = None
-        if self.world > 1:
+        if self.world > 1 or "TORCHELASTIC_RUN_ID" in os.environ:  # any torchrun launch, also with one rank
             import torch
             import torch.distributed as dist
 
             torch.cuda.set_device(self.local_rank)
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            # NCCL may announce its version on stdout while the communicator comes up; stdout
+            # is reserved for the one JSON line, so it is pointed at stderr until then.
+            sys.stdout.flush()
+            saved = os.dup(1)
+            os.dup2(2, 1)
+            try:
+                dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+                dist.barrier()
+                torch.cuda.synchronize()
+            finally:
+                sys.stdout.flush()
+                os.dup2(saved, 1)
+                os.close(saved)
             self.dist, self.torch = dist, torch
         elif gpus > 1:
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
@@ -344,6 +356,34 @@ def time_steps(job: Job, run_step, steps: int, warmup: int, sampler: ClockSample
     return job.max_over_ranks(ms), t0, t1
 
 
+def time_allgather(job: Job, dC, rows: int, N: int) -> dict:
+    """The optional exchange, timed apart from the compute: NCCL all-gather of the bf16 C row
+    shards into the full C on every rank (not part of `value`)."""
+    import torch
+
+    from aster_b200 import _native as nat
+    from aster_b200.sharding import allgather_rows
+
+    shard = torch.empty((rows, N), dtype=torch.bfloat16, device="cuda")
+    nat.call("b200_memcpy_d2d", C.c_void_p(shard.data_ptr()), dC.ptr, rows * N * 2)
+    M_total = rows * job.world
+    full = allgather_rows(shard, M_total)  # warm-up, also builds the communicator's channels
+    torch.cuda.synchronize()
+    job.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        full = allgather_rows(shard, M_total)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = job.max_over_ranks(e0.elapsed_time(e1) / reps)
+    mine = full[job.rank * rows:(job.rank + 1) * rows]
+    recv = (job.world - 1) * rows * N * 2
+    return {"ms": ms, "recv_bytes_per_rank": recv, "recv_gbs_per_rank": recv / (ms * 1e-3) / 1e9,
+            "own_shard_intact": bool(torch.equal(mine, shard)), "full_rows": int(full.shape[0])}
+
+
 def run_gemm(args, job: Job, w: dict, name: str) -> dict:
     from aster_b200 import _native as nat
     from aster_b200.dtypes import STORAGE, to_f32
@@ -466,6 +506,8 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
         "clocks": clocks,
         "verified": verified, "verify_rel_err": rel,
     }
+    if job.dist is not None and w["dtype_c"] == "bf16":
+        line["allgather"] = time_allgather(job, sets[0][2], rows, N)
     if world == 1 and job.rank == 0 and not args.no_cpu_baseline:
         secs, reps, used = cpu_gemm_seconds(w, rows, 12.0, 5)
         line["cpu_baseline"] = {
@@ -560,7 +602,7 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
 # DRAM bytes (read + write) per launch of the dominant kernel from the ncu captures summarised
 # under profiles/ (null where no capture exists for the workload).
 TRAFFIC_BYTES: dict = {
-    "bf16_4096": 99.4e6,  # profiles/gemm_tn_kernel_bf16_4096.md: 85.4 MB read + 14.0 MB written per launch
+    "bf16_4096": 99.4e6,  # ncu capture summarised under profiles/: 85.4 MB read + 14.0 MB written per launch
 }
 
 

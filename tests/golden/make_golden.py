@@ -3,7 +3,7 @@
 Run in a container that has the reference checkout (it cannot run where the reference is
 absent; the committed JSON is what the tests read):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the iree-org/aster checkout>
 
 It imports, read-only, ``kittens.gemm_config``, ``kittens_helpers``, ``bench_harness`` from the
 reference tree, evaluates them on fixed inputs and records the outputs: labels and resource
@@ -157,4 +157,6 @@ def main(ref: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path to the iree-org/aster checkout>")
+    main(sys.argv[1])

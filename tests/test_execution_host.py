@@ -53,6 +53,7 @@ class FakeNative:
 def fake(monkeypatch):
     f = FakeNative()
     monkeypatch.setattr(nat, "call", f)
+    monkeypatch.setattr(nat, "init_current", lambda: f("b200_init", 0) or 0)
     return f
 
 
