@@ -55,6 +55,11 @@ def allgather_rows(c_shard, M: int, group=None):
 
     world = dist.get_world_size(group)
     sizes = [shard_rows(M, world, r)[1] for r in range(world)]
+    # The exchange moves bytes: bf16 bit patterns held as 16-bit integers (a type NCCL's
+    # process group rejects) travel as uint8 and are viewed back afterwards.
+    dtype = c_shard.dtype
+    if dtype in (torch.int16, torch.uint16):
+        return allgather_rows(c_shard.contiguous().view(torch.uint8), M, group).view(dtype)
     n = c_shard.shape[1]
     if len(set(sizes)) == 1:
         full = torch.empty((M, n), dtype=c_shard.dtype, device=c_shard.device)

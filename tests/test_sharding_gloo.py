@@ -55,11 +55,13 @@ def _rank_main(rank, world, port, M, N, K, out):
         first, rows = shard_rows(M, world, rank)
         a = orc.encode(sharded_uniform_rows(4, first, rows, K, block_rows=256), "bf16")
         b = orc.encode(np.random.default_rng(5).uniform(-1, 1, (N, K)).astype(np.float32), "bf16")
-        c_shard = orc.decode(orc.gemm(a, b, "bf16", "bf16"), "bf16")
-        full = allgather_rows(torch.from_numpy(c_shard), M)
+        c_bits = orc.gemm(a, b, "bf16", "bf16")  # bf16 bit patterns, as the GPU path returns them
+        full_bits = allgather_rows(torch.from_numpy(c_bits.view(np.int16)), M)  # 16-bit ints travel as bytes
+        full = allgather_rows(torch.from_numpy(orc.decode(c_bits, "bf16")), M)
         a_full = orc.encode(sharded_uniform_rows(4, 0, M, K, block_rows=256), "bf16")
-        want = orc.decode(orc.gemm(a_full, b, "bf16", "bf16"), "bf16")
-        out.put((rank, bool(np.array_equal(full.numpy(), want)), tuple(full.shape)))
+        want_bits = orc.gemm(a_full, b, "bf16", "bf16")
+        ok = np.array_equal(full.numpy(), orc.decode(want_bits, "bf16")) and np.array_equal(full_bits.numpy().view(np.uint16), want_bits)
+        out.put((rank, bool(ok), tuple(full.shape)))
     finally:
         dist.destroy_process_group()
 
