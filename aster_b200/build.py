@@ -15,7 +15,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libaster_b200.so"
-SOURCES = ["runtime.cpp", "bandwidth.cu", "gemm_sm100.cu", "gemm_noalloc.cu"]
+SOURCES = ["runtime.cpp", "nccl_rows.cpp", "bandwidth.cu", "gemm_sm100.cu", "gemm_noalloc.cu"]
 HEADERS = ["common.h", "ptx_sm100.cuh", "gemm_kernel.cuh", "../../include/aster_b200.h"]
 
 NVCC_FLAGS = [

@@ -66,7 +66,8 @@ struct Params {
   int stages;
   int raster_group;    // m-blocks per rasterisation group
   uint32_t idesc;
-  int kind_f8;
+  int mma_kind;        // sm100::MmaKind
+  int acc_int;         // s32 accumulators (8-bit integer inputs): 1 = convert to float for the epilogue, 2 = store as they are
   int relu;
   int bias_axis;       // 0 = per column (N), 1 = per row (M)
   const float* bias;   // may be null
@@ -480,7 +481,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t empty_addr = empty_bar(0);
       const uint32_t peer_delta = CG == 2 ? map_to_cta(bar_base, 1u) - bar_base : 0u;  // same offset in the peer CTA
       const bool do_mma = (p.debug_mode & 3) != 2;
-      const bool kind_f8 = p.kind_f8 != 0;
+      const int mma_kind = p.mma_kind;
       const uint32_t idesc = p.idesc;
       const int stages = p.stages;
       for (int item = first_item; ok && item < num_items; item += item_stride) {
@@ -500,7 +501,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           tc_fence_after_sync();
           if (elect_one()) {
-            if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, kind_f8);
+            if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, mma_kind);
             umma_commit<CG>(empty_addr);
             if constexpr (CG == 2) umma_commit<CG>(empty_addr + peer_delta);
           }
@@ -621,8 +622,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           continue;
         }
+        if (p.acc_int != 0) {
+          // Integer accumulators never take part in a K split (the plan refuses it).
+          if (p.acc_int == 2) {
+            // The 32-bit words are moved, not converted: C receives the s32 sums bit for bit.
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+            if (row_ok) store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid);
+            continue;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = static_cast<float>(static_cast<int>(v[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+        }
         if (w.part == 0 && exchange) {
           // The first contributor's chunk was fetched one iteration ahead (`ahead`); further
           // contributors, if any, are read in place.

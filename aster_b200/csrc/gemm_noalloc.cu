@@ -156,8 +156,8 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
   p.split_k = split;
   p.stages = kStages;
   p.raster_group = 8;
-  p.idesc = sm100::make_idesc(dtype_ab == B200_BF16 ? 1u : 0u, gemm::kBM, kTileN);
-  p.kind_f8 = dtype_ab == B200_E4M3 ? 1 : 0;
+  p.idesc = sm100::make_idesc(1u, dtype_ab == B200_BF16 ? 1u : 0u, dtype_ab == B200_BF16 ? 1u : 0u, gemm::kBM, kTileN);
+  p.mma_kind = dtype_ab == B200_E4M3 ? sm100::kKindF8 : sm100::kKindF16;
   p.C = C;
   p.workspace = setup->scratch;  // the device address from cudaGetSymbolAddress, never the symbol itself
   p.status = setup->status;

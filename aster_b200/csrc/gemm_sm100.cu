@@ -82,7 +82,7 @@ KernelFn select_kernel_cg(int bn, bool f32) {
 }
 
 KernelFn select_kernel(int bn, int dtype_c, int cta_group) {
-  const bool f32 = dtype_c == B200_F32;
+  const bool f32 = dtype_c == B200_F32 || dtype_c == B200_I32;  // 32-bit outputs share the store path
   return cta_group == 2 ? select_kernel_cg<2>(bn, f32) : select_kernel_cg<1>(bn, f32);
 }
 
@@ -90,11 +90,34 @@ int elt_bytes(int dtype) {
   switch (dtype) {
     case B200_F16:
     case B200_BF16: return 2;
-    case B200_E4M3: return 1;
-    case B200_F32: return 4;
+    case B200_E4M3:
+    case B200_E5M2:
+    case B200_E5M2_E4M3:
+    case B200_E4M3_E5M2:
+    case B200_I8: return 1;
+    case B200_F32:
+    case B200_I32: return 4;
     default: return 0;
   }
 }
+
+bool is_f8(int dtype) { return dtype == B200_E4M3 || dtype == B200_E5M2 || dtype == B200_E5M2_E4M3 || dtype == B200_E4M3_E5M2; }
+
+// tcgen05 instruction descriptor for the plan's operand types and MMA shape.
+uint32_t idesc_for(int dtype_ab, uint32_t umma_m, uint32_t umma_n) {
+  uint32_t d_fmt = 1u, a_fmt = 0u, b_fmt = 0u;  // f32 accumulators, f16 / e4m3 inputs
+  switch (dtype_ab) {
+    case B200_BF16: a_fmt = b_fmt = 1u; break;
+    case B200_E5M2: a_fmt = b_fmt = 1u; break;
+    case B200_E5M2_E4M3: a_fmt = 1u; break;
+    case B200_E4M3_E5M2: b_fmt = 1u; break;
+    case B200_I8: d_fmt = 2u; a_fmt = b_fmt = 1u; break;  // signed 8-bit, s32 accumulators
+    default: break;
+  }
+  return sm100::make_idesc(d_fmt, a_fmt, b_fmt, umma_m, umma_n);
+}
+
+int mma_kind_for(int dtype_ab) { return dtype_ab == B200_I8 ? sm100::kKindI8 : (is_f8(dtype_ab) ? sm100::kKindF8 : sm100::kKindF16); }
 
 constexpr int kMaxSmemOptin = 232448;  // 227 KB: the sm_100 per-block opt-in limit
 constexpr int kDefaultSms = 148;
@@ -205,6 +228,7 @@ void plan_tail_split(b200_gemm_plan* plan) {
   plan->tail_tiles = plan->tail_parts = plan->tail_kb0 = plan->tail_kb = 0;
   plan->tail_ws_bytes = plan->tail_flag_bytes = 0;
   if (plan->split_k > 1 || plan->desc.reserved[1] == 1) return;  // reserved[1] = 1: caller opted out
+  if (plan->desc.dtype_ab == B200_I8) return;  // partial tiles are exchanged as fp32; s32 sums stay whole
   const int units = plan->units_cap;
   const int tiles = plan->m_blocks * plan->n_blocks;
   if (units < 2 || tiles < 1) return;
@@ -321,6 +345,8 @@ int check_run_args(const b200_gemm_plan* plan, const void* A, const void* B, con
 int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const float* bias, const float* scale_a,
            const float* scale_b, void* workspace, size_t workspace_size, cudaStream_t stream) {
   const b200_gemm_desc& d = plan->desc;
+  B200_REQUIRE(d.dtype_c != B200_I32 || (scale_a == nullptr && scale_b == nullptr),
+               "gemm_run: i32 output carries the integer sums unchanged; scales need f32 or bf16 output");
   if (plan->map_a_ptr != A) {
     int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);  // per CTA
     if (rc != B200_OK) return rc;
@@ -349,9 +375,9 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.split_k = plan->split_k;
   p.stages = plan->stages;
   p.raster_group = plan->raster_group;
-  p.kind_f8 = d.dtype_ab == B200_E4M3 ? 1 : 0;
-  p.idesc = sm100::make_idesc(d.dtype_ab == B200_BF16 ? 1u : 0u, static_cast<uint32_t>(gemm::kBM * plan->cg),
-                              static_cast<uint32_t>(plan->bn));
+  p.mma_kind = mma_kind_for(d.dtype_ab);
+  p.acc_int = d.dtype_ab == B200_I8 ? (d.dtype_c == B200_I32 ? 2 : 1) : 0;
+  p.idesc = idesc_for(d.dtype_ab, static_cast<uint32_t>(gemm::kBM * plan->cg), static_cast<uint32_t>(plan->bn));
   p.relu = (d.epilogue == B200_EPI_BIAS_RELU || d.epilogue == B200_EPI_RELU) ? 1 : 0;
   p.bias_axis = d.bias_axis;
   p.bias = (d.epilogue == B200_EPI_BIAS_RELU || d.epilogue == B200_EPI_BIAS) ? bias : nullptr;
@@ -429,9 +455,15 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
                (long long)d.M, (long long)d.N, (long long)d.K);
   B200_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256 && d.K < (1ll << 31) - 256,
                "gemm_plan_create: each of M, N, K must be below 2^31");
-  B200_REQUIRE(d.dtype_ab == B200_F16 || d.dtype_ab == B200_BF16 || d.dtype_ab == B200_E4M3,
-               "gemm_plan_create: dtype_ab=%d is not f16, bf16 or e4m3", d.dtype_ab);
-  B200_REQUIRE(d.dtype_c == B200_F32 || d.dtype_c == B200_BF16, "gemm_plan_create: dtype_c=%d is not f32 or bf16", d.dtype_c);
+  B200_REQUIRE(d.dtype_ab == B200_F16 || d.dtype_ab == B200_BF16 || is_f8(d.dtype_ab) || d.dtype_ab == B200_I8,
+               "gemm_plan_create: dtype_ab=%d is not f16, bf16, e4m3, e5m2 (or a mix of the two) or i8", d.dtype_ab);
+  B200_REQUIRE(d.dtype_c == B200_F32 || d.dtype_c == B200_BF16 || d.dtype_c == B200_I32,
+               "gemm_plan_create: dtype_c=%d is not f32, bf16 or i32", d.dtype_c);
+  B200_REQUIRE(d.dtype_c != B200_I32 || d.dtype_ab == B200_I8, "gemm_plan_create: i32 output needs i8 inputs");
+  B200_REQUIRE(d.dtype_c != B200_I32 || d.epilogue == B200_EPI_NONE,
+               "gemm_plan_create: i32 output carries the integer sums unchanged; bias, ReLU and scales need f32 or bf16 output");
+  B200_REQUIRE(d.dtype_ab != B200_I8 || d.split_k <= 1,
+               "gemm_plan_create: i8 inputs do not split K (split_k=%d): integer sums are not exchanged as fp32", d.split_k);
   B200_REQUIRE(d.b_layout >= B200_B_ROW_MAJOR_NK && d.b_layout <= B200_B_PACKED, "gemm_plan_create: bad b_layout %d", d.b_layout);
   B200_REQUIRE(d.epilogue >= B200_EPI_NONE && d.epilogue <= B200_EPI_RELU, "gemm_plan_create: bad epilogue %d", d.epilogue);
   B200_REQUIRE(d.bias_axis == B200_BIAS_AXIS_N || d.bias_axis == B200_BIAS_AXIS_M, "gemm_plan_create: bad bias_axis %d", d.bias_axis);
@@ -488,7 +520,7 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   plan->n_blocks = ceil_div(d.N, bn);
 
   int split = d.split_k <= 1 ? 1 : d.split_k;
-  if (d.split_k == -1) {
+  if (d.split_k == -1 && d.dtype_ab != B200_I8) {  // integer sums never split
     // Skinny problems: too few tiles to occupy the SMs, so cut K until they do, keeping at
     // least four K blocks per partition.
     const int64_t tiles = static_cast<int64_t>(plan->m_blocks) * plan->n_blocks;

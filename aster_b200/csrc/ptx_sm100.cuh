@@ -187,41 +187,40 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Operand kinds of tcgen05.mma used here: 16-bit floats (instruction K = 16), 8-bit floats and
+// 8-bit integers (K = 32: always 32 bytes of K per instruction).
+enum MmaKind : int { kKindF16 = 0, kKindF8 = 1, kKindI8 = 2 };
+
 // D[tmem] (+)= A[smem] * B[smem]^T for one instruction-K slice.  `accumulate` = 0 overwrites D.
-// KIND_F8 selects kind::f8f6f4 (8-bit inputs, K = 32) instead of kind::f16 (16-bit, K = 16).
+#define B200_MMA_ONE_ASM(GROUP, KIND)                                                           \
+  asm volatile(                                                                                 \
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"                                              \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), \
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)                                     \
+      : "memory")
+
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate, bool kind_f8) {
+                                        uint32_t accumulate, int kind) {
   if constexpr (CTA_GROUP == 1) {
-    if (kind_f8) {
-      asm volatile(
-          "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-          "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-          "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-          : "memory");
+    if (kind == kKindF8) {
+      B200_MMA_ONE_ASM("1", "f8f6f4");
+    } else if (kind == kKindI8) {
+      B200_MMA_ONE_ASM("1", "i8");
     } else {
-      asm volatile(
-          "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-          "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-          "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-          : "memory");
+      B200_MMA_ONE_ASM("1", "f16");
     }
   } else {
-    if (kind_f8) {
-      asm volatile(
-          "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-          "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-          "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-          : "memory");
+    if (kind == kKindF8) {
+      B200_MMA_ONE_ASM("2", "f8f6f4");
+    } else if (kind == kKindI8) {
+      B200_MMA_ONE_ASM("2", "i8");
     } else {
-      asm volatile(
-          "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-          "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-          "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-          : "memory");
+      B200_MMA_ONE_ASM("2", "f16");
     }
   }
 }
+#undef B200_MMA_ONE_ASM
 
 // The four MMAs of one pipeline stage in a single instruction sequence: D (+)= A_k . B_k^T for
 // the four 32-byte K slices of a 128-byte-swizzled stage.  `a_lo` / `b_lo` are the low words of
@@ -262,16 +261,20 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64
 
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_stage(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
-                                           uint32_t accumulate_first, bool kind_f8) {
+                                           uint32_t accumulate_first, int kind) {
   if constexpr (CTA_GROUP == 1) {
-    if (kind_f8) {
+    if (kind == kKindF8) {
       B200_MMA_STAGE_ASM("1", "f8f6f4");
+    } else if (kind == kKindI8) {
+      B200_MMA_STAGE_ASM("1", "i8");
     } else {
       B200_MMA_STAGE_ASM("1", "f16");
     }
   } else {
-    if (kind_f8) {
+    if (kind == kKindF8) {
       B200_MMA_STAGE_ASM("2", "f8f6f4");
+    } else if (kind == kKindI8) {
+      B200_MMA_STAGE_ASM("2", "i8");
     } else {
       B200_MMA_STAGE_ASM("2", "f16");
     }
@@ -294,12 +297,13 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   }
 }
 
-// Instruction descriptor for kind::f16 / kind::f8f6f4, fp32 accumulator, both operands K-major.
-//   bits 4-5 D format (1 = f32)   bits 7-9 A format   bits 10-12 B format
-//   bits 17-22 N >> 3             bits 24-28 M >> 4
-// Formats: kind::f16 0 = f16, 1 = bf16; kind::f8f6f4 0 = e4m3.
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t umma_m, uint32_t umma_n) {
-  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
+// Instruction descriptor, both operands K-major.
+//   bits 4-5 D format (1 = f32, 2 = s32)   bits 7-9 A format   bits 10-12 B format
+//   bits 17-22 N >> 3                      bits 24-28 M >> 4
+// Formats: kind::f16 0 = f16, 1 = bf16; kind::f8f6f4 0 = e4m3, 1 = e5m2; kind::i8 0 = u8, 1 = s8.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t d_format, uint32_t a_format, uint32_t b_format, uint32_t umma_m,
+                                                  uint32_t umma_n) {
+  return (d_format << 4) | (a_format << 7) | (b_format << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
 }
 
 // Load 32 consecutive fp32 columns of this thread's TMEM lane (warp w may touch lanes

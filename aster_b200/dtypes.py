@@ -1,8 +1,10 @@
 """Host-side storage helpers for the element types numpy lacks.
 
-bf16 travels as ``uint16`` bit patterns and fp8-e4m3 (OCP "e4m3fn": bias 7, no infinities, max
-finite 448, 0x7F/0xFF = NaN) as ``uint8``.  Conversions are round-to-nearest-even, the rounding
-the GPU epilogue (``cvt.rn``) and the tensor cores' operand formats assume.
+bf16 travels as ``uint16`` bit patterns, fp8-e4m3 (OCP "e4m3fn": bias 7, no infinities, max
+finite 448, 0x7F/0xFF = NaN) and fp8-e5m2 (OCP: bias 15, the upper byte of an IEEE half, max
+finite 57344; "bf8" in the reference's MFMA names) as ``uint8``.  8-bit integers are ``int8``
+and their sums ``int32``.  Conversions are round-to-nearest-even, the rounding the GPU epilogue
+(``cvt.rn``) and the tensor cores' operand formats assume.
 """
 
 from __future__ import annotations
@@ -10,6 +12,7 @@ from __future__ import annotations
 import numpy as np
 
 E4M3_MAX = 448.0
+E5M2_MAX = 57344.0
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -83,6 +86,28 @@ def f32_to_e4m3_bits(x: np.ndarray) -> np.ndarray:
     return bits.astype(np.uint8)
 
 
+def e5m2_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    """fp8-e5m2 bit patterns (uint8) -> float32 (exact): the byte is the top half of an f16."""
+    b = np.ascontiguousarray(b, dtype=np.uint8)
+    return (b.astype(np.uint16) << np.uint16(8)).view(np.float16).astype(np.float32)
+
+
+def f32_to_e5m2_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> fp8-e5m2 bit patterns (uint8), round-to-nearest-even in one step (not through
+    f16, which would round twice).  Magnitudes beyond 57344 saturate to it; NaN -> 0x7F."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    a = np.abs(x).astype(np.float64)
+    a = np.where(np.isnan(a), 0.0, a)
+    _, ex = np.frexp(a)
+    e = np.maximum(ex - 1, -14)  # subnormals share binade -14
+    step = np.ldexp(1.0, e - 2)
+    q = np.minimum(np.rint(a / step) * step, E5M2_MAX)
+    bits = (q.astype(np.float16).view(np.uint16) >> np.uint16(8)).astype(np.int64)  # q is exact in f16
+    bits = bits | np.where(np.signbit(x), 0x80, 0)
+    bits = np.where(np.isnan(x), 0x7F, bits)
+    return bits.astype(np.uint8)
+
+
 def quantize_e4m3(x: np.ndarray) -> tuple[np.ndarray, np.float32]:
     """Per-tensor scaled quantisation: ``scale = amax / 448``, ``q = e4m3(x / scale)``.
 
@@ -102,6 +127,10 @@ def to_f32(arr: np.ndarray, dtype: str) -> np.ndarray:
         return bf16_bits_to_f32(arr)
     if dtype == "e4m3":
         return e4m3_bits_to_f32(arr)
+    if dtype == "e5m2":
+        return e5m2_bits_to_f32(arr)
+    if dtype in ("i8", "i32"):
+        return np.asarray(arr).astype(np.float32)
     if dtype == "f32":
         return np.asarray(arr, dtype=np.float32)
     raise ValueError(f"unknown dtype {dtype!r}")
@@ -115,9 +144,16 @@ def from_f32(x: np.ndarray, dtype: str) -> np.ndarray:
         return f32_to_bf16_bits(x)
     if dtype == "e4m3":
         return f32_to_e4m3_bits(x)
+    if dtype == "e5m2":
+        return f32_to_e5m2_bits(x)
+    if dtype == "i8":
+        return np.clip(np.rint(np.asarray(x, dtype=np.float32)), -128, 127).astype(np.int8)
+    if dtype == "i32":
+        return np.rint(np.asarray(x, dtype=np.float64)).astype(np.int32)
     if dtype == "f32":
         return np.ascontiguousarray(x, dtype=np.float32)
     raise ValueError(f"unknown dtype {dtype!r}")
 
 
-STORAGE = {"f16": np.float16, "bf16": np.uint16, "e4m3": np.uint8, "f32": np.float32}
+STORAGE = {"f16": np.float16, "bf16": np.uint16, "e4m3": np.uint8, "e5m2": np.uint8, "i8": np.int8, "i32": np.int32,
+           "f32": np.float32}

@@ -17,7 +17,8 @@ from . import _native as nat
 from .dtypes import STORAGE
 from .execution import GpuBuffer
 
-DTYPE_CODES = {"f16": nat.F16, "bf16": nat.BF16, "e4m3": nat.E4M3, "f32": nat.F32}
+DTYPE_CODES = {"f16": nat.F16, "bf16": nat.BF16, "e4m3": nat.E4M3, "f32": nat.F32, "e5m2": nat.E5M2, "i8": nat.I8,
+               "i32": nat.I32, "e5m2_e4m3": nat.E5M2_E4M3, "e4m3_e5m2": nat.E4M3_E5M2}
 B_LAYOUT_CODES = {"row_major": nat.B_ROW_MAJOR_NK, "ref_preshuffled": nat.B_REF_PRESHUFFLED, "packed": nat.B_PACKED}
 EPILOGUE_CODES = {"none": nat.EPI_NONE, "bias_relu": nat.EPI_BIAS_RELU, "bias": nat.EPI_BIAS, "relu": nat.EPI_RELU}
 BIAS_AXIS_CODES = {"n": nat.BIAS_AXIS_N, "m": nat.BIAS_AXIS_M}
@@ -213,20 +214,22 @@ def gemm(
 ) -> np.ndarray:
     """``C = epilogue(A . B^T)`` on the GPU with host arrays in and a host array out.
 
-    A is ``[M, K]``, B is ``[N, K]`` (both K-contiguous), stored as float16, or as bf16 /
-    e4m3 bit patterns (uint16 / uint8; see :mod:`aster_b200.dtypes`).  ``B`` in a direct-B
+    A is ``[M, K]``, B is ``[N, K]`` (both K-contiguous), stored as float16, as bf16 / e4m3 /
+    e5m2 bit patterns (uint16 / uint8; see :mod:`aster_b200.dtypes`) or as int8.  ``B`` in a direct-B
     layout ("ref_preshuffled" or "packed" = row-major to be packed) is packed on the device
     first.  ``tail_split=True`` lends the plan its optional workspace so that a mostly idle
     last round of tiles is cut along K (changes the fp32 summation order of those tiles).
-    Returns ``[M, N]`` float32, or bf16 bit patterns (uint16) for ``dtype_c="bf16"``.
+    Returns ``[M, N]`` float32, bf16 bit patterns (uint16) for ``dtype_c="bf16"``, or the int32
+    sums for int8 inputs with ``dtype_c="i32"``.
     """
     if shape is None:
         M, K = A.shape
         N = B.shape[0]
     else:
         M, N, K = shape
-    A = _check_operand("A", A, (M, K), dtype_ab)
-    B = _check_operand("B", B, (N, K), dtype_ab)
+    type_a, type_b = dtype_ab.split("_")[0], dtype_ab.split("_")[-1]  # "e5m2_e4m3": A e5m2, B e4m3
+    A = _check_operand("A", A, (M, K), type_a)
+    B = _check_operand("B", B, (N, K), type_b)
     if plan is None:
         epilogue = {(False, False): "none", (True, True): "bias_relu", (True, False): "bias", (False, True): "relu"}[
             (bias is not None, bool(relu))

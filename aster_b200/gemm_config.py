@@ -480,10 +480,10 @@ class WeakScaledMappedGemmInstance:
 # ---------------------------------------------------------------------------------------------
 # B200 reading of an instance
 # ---------------------------------------------------------------------------------------------
-_ELT_BYTES = {"f16": 2, "bf16": 2, "e4m3": 1, "f32": 4}
+_ELT_BYTES = {"f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "i8": 1, "f32": 4, "i32": 4}
 _LEGAL_TILE_N = (256, 128, 64, 32)
 _B200_SUFFIX_RE = re.compile(
-    r"_b200_(f16|bf16|e4m3)_o(f32|bf16)_e(none|biasrelu|bias|relu)(_bm)?(?:_bn(\d+))?(?:_st(\d+))?(?:_sk(-?\d+))?(?:_cg(\d))?$"
+    r"_b200_(f16|bf16|e4m3|e5m2|i8)_o(f32|bf16|i32)_e(none|biasrelu|bias|relu)(_bm)?(?:_bn(\d+))?(?:_st(\d+))?(?:_sk(-?\d+))?(?:_cg(\d))?$"
 )
 _EPI_TOKEN = {"none": "none", "bias_relu": "biasrelu", "bias": "bias", "relu": "relu"}
 _EPI_FROM_TOKEN = {v: k for k, v in _EPI_TOKEN.items()}
@@ -511,7 +511,8 @@ class B200GemmInstance(WeakScaledMappedGemmInstance):
                  epilogue: str = "none", bias_axis: str = "n", tile_n: int = 0, stages: Optional[int] = None, split_k: int = 0,
                  cta_group: int = 0):
         super().__init__(spec, mapping)
-        if dtype_ab not in ("f16", "bf16", "e4m3") or dtype_c not in ("f32", "bf16"):
+        if dtype_ab not in ("f16", "bf16", "e4m3", "e5m2", "i8") or dtype_c not in ("f32", "bf16", "i32") or (
+                dtype_c == "i32" and dtype_ab != "i8"):
             raise ValueError(f"unsupported element types {dtype_ab!r} -> {dtype_c!r}")
         if epilogue not in _EPI_TOKEN:
             raise ValueError(f"unknown epilogue {epilogue!r}")

@@ -90,10 +90,11 @@ def execute_multitile_hsaco(cfg: B200GemmInstance, hsaco_path: str, num_iteratio
                             scale_a: Optional[float] = None, scale_b: Optional[float] = None, flush_llc=None):
     """Run a compiled config ``num_iterations`` times; returns ``(C_flat, times_ns)``.
 
-    A is ``[M,K]`` and B ``[N,K]`` in the storage type of ``cfg.dtype_ab`` (float16, or uint16 /
-    uint8 bit patterns).  For a direct-B config B is preshuffled on the host exactly as the
+    A is ``[M,K]`` and B ``[N,K]`` in the storage type of ``cfg.dtype_ab`` (float16, uint16 /
+    uint8 bit patterns, or int8).  For a direct-B config B is preshuffled on the host exactly as the
     reference does before upload (test_102_..._directb_cdna3.py:418) and packed on the device
-    before the timed loop.  C is float32, or bf16 bit patterns when ``cfg.dtype_c == "bf16"``.
+    before the timed loop.  C is float32, bf16 bit patterns when ``cfg.dtype_c == "bf16"``, or
+    int32 when ``cfg.dtype_c == "i32"``.
     """
     if not skip_gpu_check and not system_has_gpu(MCPU):
         import pytest

@@ -71,3 +71,70 @@ def allgather_rows(c_shard, M: int, group=None):
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
     return torch.cat([p[:s] for p, s in zip(parts, sizes)], dim=0)
+
+
+class NcclRowGather:
+    """One process, several GPUs: gathers byte shards onto every GPU through the C ABI
+    (``b200_nccl_init_all`` / ``b200_allgather_rows_all``), without torch.
+
+    ``devices`` lists the CUDA device of each rank.  :meth:`allgather` takes, per rank, the
+    device address of its shard and of its full-size destination (both on that rank's GPU)
+    and enqueues the exchange on each GPU's default stream (or on ``streams``); it returns
+    once the work is enqueued.  The shard may already sit in its own slot of the destination.
+    """
+
+    def __init__(self, devices) -> None:
+        import ctypes as C
+
+        from . import _native as nat
+
+        self._nat, self._C = nat, C
+        self.devices = [int(d) for d in devices]
+        self._comm = None
+        comm = C.c_void_p()
+        nat.call("b200_nccl_init_all", len(self.devices), (C.c_int * len(self.devices))(*self.devices), C.byref(comm))
+        self._comm = comm.value
+
+    @staticmethod
+    def version() -> int:
+        import ctypes as C
+
+        from . import _native as nat
+
+        v = C.c_int(0)
+        nat.call("b200_nccl_version", C.byref(v))
+        return v.value
+
+    def allgather(self, c_shards, c_fulls, bytes_per_rank: int, streams=None) -> None:
+        C, n = self._C, len(self.devices)
+        if self._comm is None:
+            raise RuntimeError("communicator already destroyed")
+        if len(c_shards) != n or len(c_fulls) != n or (streams is not None and len(streams) != n):
+            raise ValueError(f"expected {n} shard, destination and stream entries")
+
+        def addr(x):
+            return getattr(x, "ptr_value", None) or int(getattr(x, "value", x) or 0)
+
+        arr = C.c_void_p * n
+        self._nat.call(
+            "b200_allgather_rows_all", C.c_void_p(self._comm), arr(*[addr(x) for x in c_shards]),
+            arr(*[addr(x) for x in c_fulls]), int(bytes_per_rank),
+            None if streams is None else arr(*[addr(s) for s in streams]),
+        )
+
+    def destroy(self) -> None:
+        if self._comm is not None:
+            comm, self._comm = self._comm, None
+            self._nat.call("b200_nccl_destroy", self._C.c_void_p(comm))
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.destroy()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass

@@ -99,7 +99,16 @@ int b200_flush_l2(void* stream);
 /* (the "run"): contrib/kittens/test/test_102_gemm_python_multitile_lds_cdna3.py:391-436.      */
 /* ------------------------------------------------------------------------------------------ */
 
-enum { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3 };
+enum {
+  B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3,
+  /* Further operand types of the reference's MFMA list (include/aster/Dialect/AMDGCN/IR/
+   * Instructions/MMA.td:138-375 bf8 and fp8/bf8 mixes, :636-727 i8 with i32 accumulators). */
+  B200_E5M2 = 4,      /* OCP e5m2 ("bf8") for A and B                                          */
+  B200_I8 = 5,        /* signed 8-bit integers, 32-bit integer accumulation                    */
+  B200_I32 = 6,       /* dtype_c only, with B200_I8 inputs: the integer sums, unchanged        */
+  B200_E5M2_E4M3 = 7, /* A e5m2, B e4m3                                                        */
+  B200_E4M3_E5M2 = 8  /* A e4m3, B e5m2                                                        */
+};
 /* Layout of the B operand handed to b200_pack_b / b200_gemm_run. */
 enum {
   B200_B_ROW_MAJOR_NK = 0,    /* B[N,K], K contiguous (reference OperandPath.LDS)                 */
@@ -111,8 +120,8 @@ enum { B200_BIAS_AXIS_N = 0, B200_BIAS_AXIS_M = 1 };
 
 typedef struct b200_gemm_desc {
   int64_t M, N, K;
-  int32_t dtype_ab;  /* B200_F16 | B200_BF16 | B200_E4M3                                        */
-  int32_t dtype_c;   /* B200_F32 | B200_BF16                                                    */
+  int32_t dtype_ab;  /* B200_F16 | B200_BF16 | B200_E4M3 | B200_E5M2 | the two mixes | B200_I8   */
+  int32_t dtype_c;   /* B200_F32 | B200_BF16 | B200_I32 (i8 inputs, no epilogue, no scales)     */
   int32_t b_layout;  /* B200_B_*                                                                */
   int32_t epilogue;  /* B200_EPI_*                                                              */
   int32_t bias_axis; /* B200_BIAS_AXIS_*                                                        */
@@ -229,6 +238,32 @@ int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, 
                             int num_ctas, void* stream);
 /* out[i] = max(a[i] + b[i], 0); examples/07_simple_fusion/simple_fusion.py:62-144. */
 int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void* stream);
+
+/* ---- optional: gather row shards of C onto every GPU (NCCL over NVLink) ------------------
+ * No counterpart in the reference, whose multi-GPU support is fan-out of whole configurations
+ * over worker processes (contrib/kittens/test/bench/bench_harness.py:1013-1053).  One process
+ * drives `ndev` GPUs; each GPU computes the rows [rank*M/ndev, (rank+1)*M/ndev) of C with its
+ * own plan, and these calls put all of C on every GPU.  NCCL is opened at run time (the
+ * soname libnccl.so.2, or the file ASTER_B200_NCCL_LIB names), the way the reference opens
+ * its HIP runtime (python/lib/RuntimeModule.cpp:38-116); without it every call returns
+ * B200_ERR_UNSUPPORTED.  The GEMM itself never needs these. */
+typedef struct b200_comm b200_comm;
+int b200_nccl_version(int* version);
+/* devs == NULL means devices 0..ndev-1.  The calling thread's current device is restored. */
+int b200_nccl_init_all(int ndev, const int* devs, b200_comm** comm);
+int b200_nccl_destroy(b200_comm* comm);
+/* Rank `rank` contributes `bytes_per_rank` bytes at c_shard and receives ndev*bytes_per_rank
+ * bytes at c_full (both on that rank's GPU; c_shard may be its own slot inside c_full, and no
+ * other overlap is accepted).  `stream` belongs to that rank's GPU.  A thread that issues the
+ * call for more than one rank must bracket the calls with b200_nccl_group_start/_end, or use
+ * b200_allgather_rows_all, which checks every rank's arguments before it hands any to NCCL. */
+int b200_nccl_group_start(void);
+int b200_nccl_group_end(void);
+int b200_allgather_rows(b200_comm* comm, int rank, const void* c_shard, void* c_full,
+                        size_t bytes_per_rank, void* stream);
+/* All ranks at once: arrays of ndev pointers (streams may be NULL: each GPU's default stream). */
+int b200_allgather_rows_all(b200_comm* comm, const void* const* c_shards, void* const* c_fulls,
+                            size_t bytes_per_rank, void* const* streams);
 
 #ifdef __cplusplus
 }

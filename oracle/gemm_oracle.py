@@ -13,7 +13,8 @@ known-answer tests and by fixtures generated from the reference's pure-Python la
 (paths relative to the iree-org/aster tree).
 
 Storage conventions: f16 = ``np.float16``; bf16 = ``np.uint16`` bit patterns; fp8-e4m3 (OCP
-e4m3fn) = ``np.uint8`` bit patterns.  Conversions here are written independently of the
+e4m3fn) and fp8-e5m2 (OCP; the reference's "bf8") = ``np.uint8`` bit patterns; i8 = ``np.int8``
+with ``np.int32`` sums.  Conversions here are written independently of the
 product's (``ml_dtypes`` when importable, bit arithmetic otherwise) so that tests can pit one
 against the other.
 """
@@ -81,7 +82,40 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     return code | np.where(np.signbit(x), 0x80, 0).astype(np.uint8)
 
 
+def e5m2_decode(bits: np.ndarray) -> np.ndarray:
+    bits = np.asarray(bits, dtype=np.uint8)
+    if _mld is not None:
+        return bits.view(_mld.float8_e5m2).astype(np.float32)
+    return (bits.astype(np.uint16) << 8).view(np.float16).astype(np.float32)
+
+
+def e5m2_encode(x: np.ndarray) -> np.ndarray:
+    """float32 -> e5m2 bits (uint8), round to nearest even; |x| is first clamped to 57344."""
+    x = np.clip(np.asarray(x, dtype=np.float32), -57344.0, 57344.0)
+    if _mld is not None:
+        return x.astype(_mld.float8_e5m2).view(np.uint8)
+    table = e5m2_decode(np.arange(0, 0x7C, dtype=np.uint8)).astype(np.float64)  # non-negative finite codes
+    a = np.abs(x).astype(np.float64)
+    hi = np.clip(np.searchsorted(table, a, side="left"), 0, len(table) - 1)
+    lo = np.clip(hi - 1, 0, len(table) - 1)
+    d_lo, d_hi = np.abs(a - table[lo]), np.abs(table[hi] - a)
+    code = np.where((d_hi < d_lo) | ((d_hi == d_lo) & (hi % 2 == 0)), hi, lo).astype(np.uint8)
+    return code | np.where(np.signbit(x), 0x80, 0).astype(np.uint8)
+
+
+def operand_types(dtype_ab: str):
+    """``(type of A, type of B)``: "e5m2_e4m3" and "e4m3_e5m2" mix the two 8-bit float types, as
+    the reference's v_mfma_f32_*_bf8_fp8 / _fp8_bf8 do
+    (include/aster/Dialect/AMDGCN/IR/Instructions/MMA.td:155-210)."""
+    parts = dtype_ab.split("_")
+    return (parts[0], parts[-1])
+
+
 def decode(arr: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype == "e5m2":
+        return e5m2_decode(arr)
+    if dtype in ("i8", "i32"):
+        return np.asarray(arr).astype(np.float32)
     if dtype == "f16":
         return np.asarray(arr, dtype=np.float16).astype(np.float32)
     if dtype == "bf16":
@@ -94,6 +128,8 @@ def decode(arr: np.ndarray, dtype: str) -> np.ndarray:
 
 
 def encode(x: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype == "e5m2":
+        return e5m2_encode(x)
     if dtype == "f16":
         return np.asarray(x, dtype=np.float32).astype(np.float16)
     if dtype == "bf16":
@@ -123,7 +159,17 @@ def gemm_f32(A: np.ndarray, B: np.ndarray, dtype_ab: str = "f16") -> np.ndarray:
     Exactly the reference's oracle: contrib/kittens/test/bench/bench_harness.py:821,1837;
     contrib/kittens/test/test_102_gemm_python_multitile_lds_cdna3.py:504.
     """
-    return decode(A, dtype_ab) @ decode(B, dtype_ab).T
+    ta, tb = operand_types(dtype_ab)
+    return decode(A, ta) @ decode(B, tb).T
+
+
+def gemm_i32(A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    """Exact ``int32`` product of int8 matrices (v_mfma_i32_16x16x32_i8 semantics,
+    include/aster/Dialect/AMDGCN/IR/Instructions/MMA.td:636-651): every product and partial sum
+    is an integer far below 2**53, so the float64 BLAS product is exact."""
+    acc = np.asarray(A, dtype=np.int8).astype(np.float64) @ np.asarray(B, dtype=np.int8).astype(np.float64).T
+    assert np.abs(acc).max(initial=0) < 2.0**31
+    return np.rint(acc).astype(np.int32)
 
 
 def gemm_epilogue(acc: np.ndarray, bias=None, relu: bool = False, bias_axis: str = "n", alpha: float = 1.0) -> np.ndarray:
@@ -147,8 +193,14 @@ def gemm(A, B, dtype_ab="f16", dtype_c="f32", bias=None, relu=False, bias_axis="
         alpha = np.float32(alpha) * np.float32(scale_a)
     if scale_b is not None:
         alpha = np.float32(alpha) * np.float32(scale_b)
-    x = gemm_epilogue(gemm_f32(A, B, dtype_ab), bias, relu, bias_axis, float(alpha))
-    return encode(x, dtype_c)
+    if dtype_ab == "i8":
+        acc = gemm_i32(A, B)
+        if dtype_c == "i32":
+            return acc
+        acc = acc.astype(np.float32)  # the kernel converts the s32 sums to float before the epilogue
+    else:
+        acc = gemm_f32(A, B, dtype_ab)
+    return encode(gemm_epilogue(acc, bias, relu, bias_axis, float(alpha)), dtype_c)
 
 
 def gemm_scalar_f32(A: np.ndarray, B: np.ndarray, dtype_ab: str = "f16") -> np.ndarray:

@@ -138,3 +138,22 @@ def test_compile_fn_writes_an_artifact(tmp_path, native_lib):
     (tmp_path / "bad.json").write_text("{}")
     with pytest.raises(RuntimeError):
         load_artifact(str(tmp_path / "bad.json"))
+
+
+def test_nccl_entry_points_check_arguments_without_a_gpu(native_lib):
+    """NCCL is opened at run time: with it present the version reads back, without it the call
+    says so; argument checks come before any NCCL or CUDA call."""
+    import ctypes as C
+
+    v = C.c_int(0)
+    rc = native_lib.b200_nccl_version(C.byref(v))
+    if rc == nat.OK:
+        assert v.value >= 20000
+    else:
+        assert rc == nat.ERR_UNSUPPORTED and b"NCCL runtime not available" in native_lib.b200_last_error()
+    comm = C.c_void_p(123)
+    assert native_lib.b200_nccl_init_all(0, None, C.byref(comm)) == nat.ERR_INVALID and comm.value is None
+    assert b"ndev 0 out of range" in native_lib.b200_last_error()
+    assert native_lib.b200_nccl_destroy(None) == nat.OK
+    assert native_lib.b200_allgather_rows(None, 0, None, None, 16, None) == nat.ERR_INVALID
+    assert b"comm is NULL" in native_lib.b200_last_error()

@@ -71,3 +71,57 @@ def test_row_shards_allgathered_equal_the_whole(gpu):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert ok is True and shape == (M, N)
+
+
+def test_single_process_gather_through_the_c_abi(gpu):
+    """One process drives both GPUs: a plan per GPU computes its row shard, the NCCL entry
+    points of the C ABI put all of C on both, and both copies equal the one-GPU product."""
+    if nat.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from aster_b200.dtypes import from_f32
+    from aster_b200.execution import GpuBuffer
+    from aster_b200.gemm import GemmPlan, gemm
+    from aster_b200.sharding import NcclRowGather
+
+    M, N, K = 512, 384, 256
+    rows = M // 2
+    rng = np.random.default_rng(8)
+    a = from_f32(rng.uniform(-1, 1, (M, K)).astype(np.float32), "bf16")
+    b = from_f32(rng.uniform(-1, 1, (N, K)).astype(np.float32), "bf16")
+    assert NcclRowGather.version() >= 21800
+    keep, fulls, shards = [], [], []
+    try:
+        for d in (0, 1):
+            nat.call("b200_set_device", d)
+            da, db, full = GpuBuffer(rows * K * 2), GpuBuffer(N * K * 2), GpuBuffer(M * N * 2)
+            da.copy_from_host(a[d * rows:(d + 1) * rows])
+            db.copy_from_host(b)
+            full.zero()
+            plan = GemmPlan(rows, N, K, "bf16", "bf16", tile_n=128)
+            if d == 0:  # rank 0 writes its shard straight into its slot of the destination
+                plan.run(da, db, full.ptr_value)
+                shards.append(full.ptr_value)
+            else:       # rank 1 gathers from a separate buffer
+                shard = GpuBuffer(rows * N * 2)
+                plan.run(da, db, shard)
+                shards.append(shard)
+                keep.append(shard)
+            nat.call("b200_device_synchronize")
+            keep += [da, db, plan]
+            fulls.append(full)
+        with NcclRowGather([0, 1]) as gather:
+            with pytest.raises(nat.B200Error, match="overlaps"):  # refused before NCCL sees any rank
+                gather.allgather([fulls[0].ptr_value + 64, shards[1]], fulls, rows * N * 2)
+            gather.allgather(shards, fulls, rows * N * 2)
+            got = []
+            for d in (0, 1):
+                nat.call("b200_set_device", d)
+                nat.call("b200_device_synchronize")
+                host = np.empty((M, N), dtype=np.uint16)
+                fulls[d].copy_to_host(host)
+                got.append(host)
+    finally:
+        nat.call("b200_set_device", 0)
+    whole = gemm(a, b, dtype_ab="bf16", dtype_c="bf16", tile_n=128).view(np.uint16)
+    assert np.array_equal(got[0], whole) and np.array_equal(got[1], whole)

@@ -170,3 +170,22 @@ class TestElementTypes:
         q = orc.decode(orc.gemm(qa, qb, "e4m3", "f32", scale_a=sa, scale_b=sb), "f32")
         rel = orc.rel_frobenius(q, a @ b.T)
         assert 0.02 < rel < 0.06
+
+
+def test_e5m2_and_int8_conversions_and_oracle():
+    """Product-side e5m2 conversion against the oracle's (ml_dtypes when present) on every code
+    and on random values; integer oracle against an int64 product."""
+    from aster_b200 import dtypes as dt
+
+    codes = np.arange(256, dtype=np.uint8)
+    a, b = dt.e5m2_bits_to_f32(codes), orc.e5m2_decode(codes)
+    assert np.array_equal(np.isnan(a), np.isnan(b)) and np.array_equal(a[~np.isnan(a)], b[~np.isnan(b)])
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(50000) * rng.choice([1e-6, 1e-3, 1.0, 100.0, 2e4], 50000)).astype(np.float32)
+    x = np.concatenate([x, a[np.isfinite(a)], np.float32([0.0, -0.0, 2.0**-16, 2.0**-17, 1.5 * 2.0**-16, 57344.0, 1e9, -1e9])])
+    assert np.array_equal(dt.f32_to_e5m2_bits(x), orc.e5m2_encode(x))
+    ia = rng.integers(-128, 128, (24, 96), dtype=np.int8)
+    ib = rng.integers(-128, 128, (40, 96), dtype=np.int8)
+    assert np.array_equal(orc.gemm_i32(ia, ib), (ia.astype(np.int64) @ ib.astype(np.int64).T).astype(np.int32))
+    assert np.array_equal(orc.gemm(ia, ib, "i8", "i32"), orc.gemm_i32(ia, ib))
+    assert orc.operand_types("e5m2_e4m3") == ("e5m2", "e4m3") and orc.operand_types("bf16") == ("bf16", "bf16")
