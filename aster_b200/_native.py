@@ -29,7 +29,7 @@ STATUS_NAMES = {
 }
 
 # Element types and enums.
-F16, BF16, E4M3, F32, E5M2, I8, I32, E5M2_E4M3, E4M3_E5M2 = range(9)
+F16, BF16, E4M3, F32, E5M2, I8, I32, E5M2_E4M3, E4M3_E5M2, MXE4M3, MXE5M2 = range(11)
 B_ROW_MAJOR_NK, B_REF_PRESHUFFLED, B_PACKED = 0, 1, 2
 EPI_NONE, EPI_BIAS_RELU, EPI_BIAS, EPI_RELU = 0, 1, 2, 3
 BIAS_AXIS_N, BIAS_AXIS_M = 0, 1
@@ -156,6 +156,9 @@ SIGNATURES = {
     "b200_vector_add_f32": [_P, _P, _P, _SZ, _P],
     "b200_copy_2d_padded_f32": [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, _P],
     "b200_add_relu_f32": [_P, _P, _P, _SZ, _P],
+    "b200_mx_scales_bytes": [C.c_int64, C.c_int64, C.POINTER(_SZ)],
+    "b200_pack_mx_scales": [_P, _P, C.c_int64, C.c_int64, _P],
+    "b200_gemm_plan_set_mx_scales": [_P, _P, _P],
     "b200_nccl_version": [C.POINTER(C.c_int)],
     "b200_nccl_init_all": [C.c_int, C.POINTER(C.c_int), C.POINTER(_P)],
     "b200_nccl_destroy": [_P],

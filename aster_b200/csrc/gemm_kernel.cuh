@@ -74,6 +74,12 @@ struct Params {
   const float* scale_a;
   const float* scale_b;
   void* C;
+  // Block-scaled kernels: E8M0 scales of A and B in blocks of [128 rows][4 K blocks] (row r of a
+  // block at byte (r % 32) * 16 + (r / 32) * 4), ordered [row block][K stage]; sf_k_stages =
+  // ceil(K / 128) blocks per row block.
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int sf_k_stages;
   const void* b_packed;  // non-null: B comes as packed tile images, streamed with 1-D bulk copies
   float* workspace;      // split-K partial sums [split][M][N] fp32
   uint32_t* status;
@@ -93,14 +99,25 @@ struct Params {
   unsigned wait_limit_ms;  // limit of every bounded wait; 0 = default
 };
 
-__host__ __device__ constexpr int stage_bytes(int bn, int cg = 1) { return (kBM + bn / cg) * kRowBytes; }
+// Block-scaled (MX) stages carry the E8M0 scales of their 128 elements of K behind the operand
+// tiles: one 512-byte block for the 128 rows of A and one per 128 rows of B, padded so that
+// the next stage stays 1024-byte aligned.
+constexpr int kScaleBlockBytes = 512;  // 128 rows x 4 K blocks of 32
+__host__ __device__ constexpr int scale_stage_bytes(int bn) { return (kScaleBlockBytes * (1 + bn / 128) + 1023) / 1024 * 1024; }
+__host__ __device__ constexpr int stage_bytes(int bn, int cg = 1, bool mx = false) {
+  return (kBM + bn / cg) * kRowBytes + (mx ? scale_stage_bytes(bn) : 0);
+}
 // Barrier block that follows the stage ring: full[8], empty[8], acc_full[2], acc_empty[2],
 // drain, TMEM base slot, abort flag.
 constexpr int kBarrierBytes = 256;
-__host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1) {
-  return stages * stage_bytes(bn, cg) + kBarrierBytes + 1024;
+__host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1, bool mx = false) {
+  return stages * stage_bytes(bn, cg, mx) + kBarrierBytes + 1024;
 }
-__host__ __device__ constexpr int tmem_columns(int bn) { return 2 * bn < 32 ? 32 : 2 * bn; }  // bn is a power of two
+// Two accumulators of bn columns; a block-scaled kernel adds two sets of 16 scale columns.
+constexpr int kScaleTmemCols = 16;
+__host__ __device__ constexpr int tmem_columns(int bn, bool mx = false) {  // bn is a power of two
+  return mx ? 512 : (2 * bn < 32 ? 32 : 2 * bn);
+}
 
 // Has more than `limit` ns passed since `t0`?  A single reading of the global timer is not
 // trusted: a reading that looks like an expiry is confirmed by a second one, and a start stamp
@@ -334,7 +351,7 @@ __device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], boo
 // rings in the same shared memory.  In the pair, full[] lives in the leader and counts the
 // bytes of both CTAs' copies; empty[] and acc_full[] exist in both CTAs and the leader's
 // commits arrive on each; acc_empty[] lives in the leader and collects both CTAs' epilogues.
-template <int BN, typename OutT, int CG>
+template <int BN, typename OutT, int CG, bool MX = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
@@ -344,8 +361,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr uint32_t kBRows = BN / CG;  // B rows staged by this CTA
   constexpr uint32_t kABytes = kBM * kRowBytes;
   constexpr uint32_t kBBytes = kBRows * kRowBytes;
-  constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  constexpr uint32_t kTmemCols = tmem_columns(BN);
+  constexpr uint32_t kStageBytes = stage_bytes(BN, CG, MX);
+  constexpr uint32_t kTmemCols = tmem_columns(BN, MX);
+  static_assert(!MX || (CG == 1 && BN == 128), "block-scaled tiles: one CTA, 128 columns");
+  static_assert(!MX || 2 * BN + 2 * kScaleTmemCols <= 512, "accumulators and scales share the 512 columns");
   constexpr int kTileM = kBM * CG;
 
   extern __shared__ uint8_t smem_raw[];
@@ -429,7 +448,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else if ((p.debug_mode & 3) == 1) {
             if (leader) mbar_arrive(full_bar(stage));
           } else if constexpr (CG == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+            mbar_arrive_expect_tx(full_bar(stage), kABytes + kBBytes + (MX ? kScaleBlockBytes * (1 + BN / 128) : 0));
+            if constexpr (MX) {
+              const uint32_t sf_dst = b_dst + kBBytes;
+              // K stages beyond the data (split-K padding) carry zero-filled operands: any scale will do.
+              const size_t ks = static_cast<size_t>(min(kb0 + kb, p.sf_k_stages - 1));
+              bulk_load_1d(sf_dst, p.sfa + (static_cast<size_t>(m_blk) * p.sf_k_stages + ks) * kScaleBlockBytes, kScaleBlockBytes, full_bar(stage));
+#pragma unroll
+              for (int q = 0; q < BN / 128; ++q) {
+                bulk_load_1d(sf_dst + (1 + q) * kScaleBlockBytes,
+                             p.sfb + (static_cast<size_t>(n_blk * (BN / 128) + q) * p.sf_k_stages + ks) * kScaleBlockBytes, kScaleBlockBytes,
+                             full_bar(stage));
+              }
+            }
             tma_load_2d(a_dst, &tmap_a, full_bar(stage), k_elem, a_row);
             if (p.b_packed != nullptr) {
               const size_t blk = static_cast<size_t>(n_blk) * (static_cast<size_t>(p.num_kb) * p.split_k) + (kb0 + kb);
@@ -483,6 +514,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool do_mma = (p.debug_mode & 3) != 2;
       const int mma_kind = p.mma_kind;
       const uint32_t idesc = p.idesc;
+      [[maybe_unused]] uint32_t sf_set = 0;
       const int stages = p.stages;
       for (int item = first_item; ok && item < num_items; item += item_stride) {
         const WorkItem w = decode_item(p, item);
@@ -501,11 +533,33 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           tc_fence_after_sync();
           if (elect_one()) {
-            if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, mma_kind);
+            if constexpr (MX) {
+              // Scales of this stage: shared memory -> TMEM (alternating column sets), then the
+              // four block-scaled MMAs; tcgen05 operations of one thread execute in order.
+              const uint32_t sf_smem = smem_base + static_cast<uint32_t>(stage) * kStageBytes + kABytes + kBBytes;
+              const uint32_t sf_tmem = tmem_base + 2u * BN + sf_set * kScaleTmemCols;  // behind the two accumulators
+              if (do_mma) {
+                tmem_cp_32x128b_warpx4(sf_tmem, make_smem_desc_scales(sf_smem));
+#pragma unroll
+                for (int q = 0; q < BN / 128; ++q) {
+                  tmem_cp_32x128b_warpx4(sf_tmem + 4u + 4u * q, make_smem_desc_scales(sf_smem + (1 + q) * kScaleBlockBytes));
+                }
+                const uint64_t da = (static_cast<uint64_t>(desc_hi) << 32) | a_lo;
+                const uint64_t db = (static_cast<uint64_t>(desc_hi) << 32) | (a_lo + b_off);
+#pragma unroll
+                for (uint32_t j = 0; j < kMmasPerStage; ++j) {
+                  umma_mx_ss(tmem_d, da + 2u * j, db + 2u * j, idesc_mx_with_scale_id(idesc, j), (kb != 0 || j != 0) ? 1u : 0u, sf_tmem,
+                             sf_tmem + 4u);
+                }
+              }
+            } else {
+              if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, mma_kind);
+            }
             umma_commit<CG>(empty_addr);
             if constexpr (CG == 2) umma_commit<CG>(empty_addr + peer_delta);
           }
           __syncwarp();
+          if constexpr (MX) sf_set ^= 1u;
           ++stage;
           a_lo += kStageBytes >> 4;
           full_addr += 8u;

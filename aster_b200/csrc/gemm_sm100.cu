@@ -81,8 +81,9 @@ KernelFn select_kernel_cg(int bn, bool f32) {
   }
 }
 
-KernelFn select_kernel(int bn, int dtype_c, int cta_group) {
+KernelFn select_kernel(int bn, int dtype_c, int cta_group, bool mx) {
   const bool f32 = dtype_c == B200_F32 || dtype_c == B200_I32;  // 32-bit outputs share the store path
+  if (mx) return f32 ? gemm::gemm_tn_kernel<128, float, 1, true> : gemm::gemm_tn_kernel<128, __nv_bfloat16, 1, true>;
   return cta_group == 2 ? select_kernel_cg<2>(bn, f32) : select_kernel_cg<1>(bn, f32);
 }
 
@@ -94,6 +95,8 @@ int elt_bytes(int dtype) {
     case B200_E5M2:
     case B200_E5M2_E4M3:
     case B200_E4M3_E5M2:
+    case B200_MXE4M3:
+    case B200_MXE5M2:
     case B200_I8: return 1;
     case B200_F32:
     case B200_I32: return 4;
@@ -101,10 +104,18 @@ int elt_bytes(int dtype) {
   }
 }
 
+int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+bool is_mx(int dtype) { return dtype == B200_MXE4M3 || dtype == B200_MXE5M2; }
+
 bool is_f8(int dtype) { return dtype == B200_E4M3 || dtype == B200_E5M2 || dtype == B200_E5M2_E4M3 || dtype == B200_E4M3_E5M2; }
 
 // tcgen05 instruction descriptor for the plan's operand types and MMA shape.
 uint32_t idesc_for(int dtype_ab, uint32_t umma_m, uint32_t umma_n) {
+  if (is_mx(dtype_ab)) {
+    const uint32_t fmt = dtype_ab == B200_MXE5M2 ? 1u : 0u;
+    return sm100::make_idesc_mx(fmt, fmt, umma_m, umma_n);
+  }
   uint32_t d_fmt = 1u, a_fmt = 0u, b_fmt = 0u;  // f32 accumulators, f16 / e4m3 inputs
   switch (dtype_ab) {
     case B200_BF16: a_fmt = b_fmt = 1u; break;
@@ -168,6 +179,26 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const uint8_t* __restrict__
   }
 }
 
+// Row-major E8M0 scales [rows][K/32] -> blocks of [128 rows][4 K blocks] in the order the
+// block-scaled kernel streams them ([row block][K stage], row r of a block at byte
+// (r % 32) * 16 + (r / 32) * 4).  Positions beyond rows or K/32 get 127 (= 2^0): the operand
+// bytes they would scale are zero-filled by the loads.
+__global__ void __launch_bounds__(256) pack_mx_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, long long rows,
+                                                             long long k_blocks32, long long row_blocks, long long k_stages) {
+  const long long total = row_blocks * k_stages * gemm::kScaleBlockBytes;
+  for (long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < total;
+       g += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long blk = g / gemm::kScaleBlockBytes;
+    const int in_blk = static_cast<int>(g - blk * gemm::kScaleBlockBytes);
+    const long long rb = blk / k_stages;
+    const long long ks = blk - rb * k_stages;
+    const int r = (in_blk >> 4) + 32 * ((in_blk & 15) >> 2);
+    const long long row = rb * 128 + r;
+    const long long kb = ks * 4 + (in_blk & 3);
+    out[g] = (row < rows && kb < k_blocks32) ? in[row * k_blocks32 + kb] : static_cast<uint8_t>(127);
+  }
+}
+
 // Streams a buffer larger than the L2 so that the next kernel starts from a cold cache.
 struct FlushState {
   void* buf = nullptr;
@@ -183,6 +214,9 @@ struct b200_gemm_plan {
   b200_gemm_desc desc;
   int bn = 0;
   int cg = 1;         // CTAs per MMA: 1, or 2 for a CTA pair (cluster of two)
+  bool mx = false;    // block-scaled 8-bit floats: scales come from b200_gemm_plan_set_mx_scales
+  const uint8_t* sfa = nullptr;
+  const uint8_t* sfb = nullptr;
   int stages = 0;
   int split_k = 1;
   int grid = 0;
@@ -347,6 +381,8 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   const b200_gemm_desc& d = plan->desc;
   B200_REQUIRE(d.dtype_c != B200_I32 || (scale_a == nullptr && scale_b == nullptr),
                "gemm_run: i32 output carries the integer sums unchanged; scales need f32 or bf16 output");
+  B200_REQUIRE(!plan->mx || (plan->sfa != nullptr && plan->sfb != nullptr),
+               "gemm_run: a block-scaled plan needs its scales first (b200_gemm_plan_set_mx_scales)");
   if (plan->map_a_ptr != A) {
     int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);  // per CTA
     if (rc != B200_OK) return rc;
@@ -384,6 +420,9 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.scale_a = scale_a;
   p.scale_b = scale_b;
   p.C = C;
+  p.sfa = plan->sfa;
+  p.sfb = plan->sfb;
+  p.sf_k_stages = ceil_div(d.K, gemm::kRowBytes);
   p.b_packed = direct_b(plan) ? B : nullptr;
   p.workspace = static_cast<float*>(workspace);
   p.status = plan->status;
@@ -441,8 +480,6 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   return B200_OK;
 }
 
-int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
-
 }  // namespace
 
 extern "C" {
@@ -455,8 +492,15 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
                (long long)d.M, (long long)d.N, (long long)d.K);
   B200_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256 && d.K < (1ll << 31) - 256,
                "gemm_plan_create: each of M, N, K must be below 2^31");
-  B200_REQUIRE(d.dtype_ab == B200_F16 || d.dtype_ab == B200_BF16 || is_f8(d.dtype_ab) || d.dtype_ab == B200_I8,
-               "gemm_plan_create: dtype_ab=%d is not f16, bf16, e4m3, e5m2 (or a mix of the two) or i8", d.dtype_ab);
+  const bool mx = is_mx(d.dtype_ab);
+  B200_REQUIRE(d.dtype_ab == B200_F16 || d.dtype_ab == B200_BF16 || is_f8(d.dtype_ab) || d.dtype_ab == B200_I8 || mx,
+               "gemm_plan_create: dtype_ab=%d is not f16, bf16, e4m3, e5m2 (or a mix of the two), i8 or a block-scaled fp8", d.dtype_ab);
+  if (mx) {
+    B200_REQUIRE(d.K % 32 == 0, "gemm_plan_create: block-scaled inputs need K %% 32 == 0 (one scale per 32 elements), got K=%lld", (long long)d.K);
+    B200_REQUIRE(d.b_layout == B200_B_ROW_MAJOR_NK, "gemm_plan_create: block-scaled inputs take row-major B");
+    B200_REQUIRE(d.cta_group <= 1 && d.tile_m != 2 * gemm::kBM, "gemm_plan_create: block-scaled inputs run with cta_group=1");
+    B200_REQUIRE(d.tile_n == 0 || d.tile_n == 128, "gemm_plan_create: block-scaled inputs use tile_n=128 (got %d)", d.tile_n);
+  }
   B200_REQUIRE(d.dtype_c == B200_F32 || d.dtype_c == B200_BF16 || d.dtype_c == B200_I32,
                "gemm_plan_create: dtype_c=%d is not f32, bf16 or i32", d.dtype_c);
   B200_REQUIRE(d.dtype_c != B200_I32 || d.dtype_ab == B200_I8, "gemm_plan_create: i32 output needs i8 inputs");
@@ -504,12 +548,14 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   // deeper ring; it needs at least one full 256-row tile to pay off and row-major B.
   int cg = d.cta_group != 0 ? d.cta_group : (d.tile_m == 2 * gemm::kBM ? 2 : (d.tile_m == gemm::kBM ? 1 : 0));
   if (cg == 0) cg = (d.b_layout == B200_B_ROW_MAJOR_NK && d.M >= 2 * gemm::kBM && d.tile_n != 32) ? 2 : 1;
+  if (mx) cg = 1;
   plan->cg = cg;
+  plan->mx = mx;
   plan->m_blocks = ceil_div(d.M, gemm::kBM * cg);
 
   // Tile width: the widest tile whose tile count still fills the machine; wide tiles halve the
   // shared-memory traffic per flop, narrow ones keep more SMs busy on small problems.
-  int bn = d.tile_n;
+  int bn = mx ? 128 : d.tile_n;
   if (bn == 0) {
     const int units = kDefaultSms / cg;  // CTAs or pairs that run at once
     bn = 256;
@@ -531,20 +577,20 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   plan->num_kb = ceil_div(k_blocks, split);
   plan->total_kb = plan->num_kb * split;
 
-  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024) / gemm::stage_bytes(bn, cg);
+  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024) / gemm::stage_bytes(bn, cg, mx);
   int stages = d.stages > 0 ? d.stages : (max_stages < gemm::kMaxStages ? max_stages : gemm::kMaxStages);
   if (stages > max_stages) {
     delete plan;
     return b200::fail(B200_ERR_INVALID, "gemm_plan_create: %d stages of %d bytes exceed the %d-byte shared memory limit", stages,
-                      gemm::stage_bytes(bn, cg), kMaxSmemOptin);
+                      gemm::stage_bytes(bn, cg, mx), kMaxSmemOptin);
   }
   plan->stages = stages;
-  plan->smem = gemm::smem_bytes(bn, stages, cg);
+  plan->smem = gemm::smem_bytes(bn, stages, cg, mx);
   // Two resident CTAs would both ask for TMEM; keep the footprint above half the SM's shared
   // memory whenever two allocations (2 * tmem_columns) would not fit in the 512 columns.
-  if (2 * gemm::tmem_columns(bn) > 512 && plan->smem <= kMaxSmemOptin / 2) plan->smem = kMaxSmemOptin / 2 + 1024;
+  if (2 * gemm::tmem_columns(bn, mx) > 512 && plan->smem <= kMaxSmemOptin / 2) plan->smem = kMaxSmemOptin / 2 + 1024;
   plan->raster_group = d.raster_group > 0 ? d.raster_group : 8;
-  plan->kernel = select_kernel(bn, d.dtype_c, cg);
+  plan->kernel = select_kernel(bn, d.dtype_c, cg, mx);
   const int cap = d.max_ctas > 0 ? d.max_ctas : kDefaultSms;
   size_grid(plan, cg == 2 ? (cap / 2 < 1 ? 1 : cap / 2) : cap);
   *out = plan;
@@ -571,7 +617,7 @@ int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* ou
   out->grid_ctas = plan->grid;
   out->block_threads = gemm::kThreads;
   out->smem_bytes = plan->smem;
-  out->tmem_columns = gemm::tmem_columns(plan->bn);
+  out->tmem_columns = gemm::tmem_columns(plan->bn, plan->mx);
   out->ctas_per_sm = plan->smem > kMaxSmemOptin / 2 ? 1 : 2;
   out->num_tiles = static_cast<int64_t>(plan->m_blocks) * plan->n_blocks;
   out->workspace_bytes = workspace_bytes(plan);
@@ -601,6 +647,38 @@ int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, vo
       plan->n_blocks, plan->total_kb, plan->desc.b_layout == B200_B_REF_PRESHUFFLED ? 1 : 0);
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_mx_scales_bytes(int64_t rows, int64_t K, size_t* bytes) {
+  B200_REQUIRE(bytes != nullptr, "mx_scales_bytes: bytes is NULL");
+  B200_REQUIRE(rows >= 1 && K >= 32 && K % 32 == 0, "mx_scales_bytes: rows must be >= 1 and K a positive multiple of 32");
+  *bytes = static_cast<size_t>(ceil_div(rows, 128)) * ceil_div(K, gemm::kRowBytes) * gemm::kScaleBlockBytes;
+  return B200_OK;
+}
+
+int b200_pack_mx_scales(const void* scales_in, void* scales_packed, int64_t rows, int64_t K, void* stream) {
+  B200_REQUIRE(scales_in != nullptr && scales_packed != nullptr, "pack_mx_scales: NULL argument");
+  B200_REQUIRE(rows >= 1 && K >= 32 && K % 32 == 0, "pack_mx_scales: rows must be >= 1 and K a positive multiple of 32");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(scales_packed) & 15u) == 0, "pack_mx_scales: output must be 16-byte aligned");
+  const long long row_blocks = ceil_div(rows, 128), k_stages = ceil_div(K, gemm::kRowBytes);
+  long long blocks = (row_blocks * k_stages * gemm::kScaleBlockBytes + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  pack_mx_scales_kernel<<<static_cast<int>(blocks), 256, 0, b200::as_stream(stream)>>>(
+      static_cast<const uint8_t*>(scales_in), static_cast<uint8_t*>(scales_packed), rows, K / 32, row_blocks, k_stages);
+  b200::count_launch();
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_gemm_plan_set_mx_scales(b200_gemm_plan* plan, const void* scales_a_packed, const void* scales_b_packed) {
+  B200_REQUIRE(plan != nullptr, "gemm_plan_set_mx_scales: plan is NULL");
+  B200_REQUIRE(plan->mx, "gemm_plan_set_mx_scales: the plan's dtype_ab is not block-scaled");
+  B200_REQUIRE(scales_a_packed != nullptr && scales_b_packed != nullptr, "gemm_plan_set_mx_scales: NULL scales");
+  B200_REQUIRE(((reinterpret_cast<uintptr_t>(scales_a_packed) | reinterpret_cast<uintptr_t>(scales_b_packed)) & 15u) == 0,
+               "gemm_plan_set_mx_scales: packed scales must be 16-byte aligned");
+  plan->sfa = static_cast<const uint8_t*>(scales_a_packed);
+  plan->sfb = static_cast<const uint8_t*>(scales_b_packed);
   return B200_OK;
 }
 

@@ -306,6 +306,44 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_format, uint32_t a_
   return (d_format << 4) | (a_format << 7) | (b_format << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
 }
 
+// ---- block-scaled 8-bit floats (kind::mxf8f6f4): one E8M0 scale per 32 elements of K ----
+// Instruction descriptor of the block-scaled kinds (accumulators are always f32):
+//   bits 4-5 scale id of B   bits 7-9 A format   bits 10-12 B format   bits 17-22 N >> 3
+//   bit 23 scale format (1 = E8M0)   bits 24-28 M >> 4   bits 29-30 scale id of A
+// A scale id selects one byte of the 32-bit scale column: the scales of four consecutive
+// K blocks of 32 share a column, so the four MMAs of a 128-byte stage use ids 0..3.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_format, uint32_t b_format, uint32_t umma_m, uint32_t umma_n) {
+  return (a_format << 7) | (b_format << 10) | ((umma_n >> 3) << 17) | (1u << 23) | ((umma_m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t idesc_mx_with_scale_id(uint32_t idesc, uint32_t id) { return idesc | (id << 4) | (id << 29); }
+
+// Shared-memory descriptor of a scale block: 32 rows of 16 bytes, rows contiguous (no swizzle,
+// groups of 8 rows 128 bytes apart).
+__device__ __forceinline__ uint64_t make_smem_desc_scales(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>(16 >> 4) << 16;
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+// Copy 32 rows x 16 bytes from shared memory into four TMEM columns (row i -> lane i of each of
+// the four 32-lane quarters).  Asynchronous; ordered before later tcgen05.mma of this thread.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// D[tmem] (+)= (A * scale_a) . (B * scale_b)^T for one 32-element K block, scales in TMEM.
+__device__ __forceinline__ void umma_mx_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                           uint32_t tmem_scale_a, uint32_t tmem_scale_b) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_scale_a), "r"(tmem_scale_b)
+      : "memory");
+}
+
 // Load 32 consecutive fp32 columns of this thread's TMEM lane (warp w may touch lanes
 // 32*(w%4) .. 32*(w%4)+31; thread i of the warp reads lane base+i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {

@@ -119,6 +119,37 @@ def quantize_e4m3(x: np.ndarray) -> tuple[np.ndarray, np.float32]:
     return f32_to_e4m3_bits(x / scale), scale
 
 
+MX_BLOCK = 32  # elements of K that share one E8M0 scale
+_MX_ELEM = {"e4m3": (8, f32_to_e4m3_bits, e4m3_bits_to_f32), "e5m2": (15, f32_to_e5m2_bits, e5m2_bits_to_f32)}
+
+
+def quantize_mx(x: np.ndarray, elem: str = "e4m3") -> tuple[np.ndarray, np.ndarray]:
+    """Block-scaled ("MX") quantisation along the last axis, after the OCP microscaling rule:
+    per block of 32 values the shared exponent is ``floor(log2(amax)) - emax`` (emax = 8 for
+    e4m3, 15 for e5m2), clamped to [-127, 127]; elements are ``x / 2**exponent`` rounded to
+    nearest even with saturation.  Returns ``(bits [..., K], scales [..., K/32])``, both uint8;
+    a scale byte is the biased exponent (127 = 1.0).  An all-zero block gets scale 127."""
+    emax, enc, _ = _MX_ELEM[elem]
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    K = x.shape[-1]
+    if K % MX_BLOCK:
+        raise ValueError(f"last axis {K} is not a multiple of {MX_BLOCK}")
+    blocks = x.reshape(*x.shape[:-1], K // MX_BLOCK, MX_BLOCK)
+    amax = np.abs(blocks).max(axis=-1)
+    _, ex = np.frexp(amax)  # amax = m * 2**ex with m in [0.5, 1): floor(log2(amax)) = ex - 1
+    shared = np.clip(np.where(amax > 0, ex - 1 - emax, 0), -127, 127).astype(np.int32)
+    scaled = blocks / np.ldexp(np.float32(1.0), shared)[..., None]
+    return enc(scaled.astype(np.float32)).reshape(x.shape), (shared + 127).astype(np.uint8)
+
+
+def dequantize_mx(bits: np.ndarray, scales: np.ndarray, elem: str = "e4m3") -> np.ndarray:
+    """float32 values of block-scaled data (exact unless the product leaves the f32 range)."""
+    _, _, dec = _MX_ELEM[elem]
+    vals = dec(bits)
+    factor = np.ldexp(np.float32(1.0), np.asarray(scales, dtype=np.int32) - 127)
+    return (vals.reshape(*scales.shape, MX_BLOCK) * factor[..., None]).reshape(vals.shape).astype(np.float32)
+
+
 def to_f32(arr: np.ndarray, dtype: str) -> np.ndarray:
     """Decode a stored operand (see module docstring) to float32."""
     if dtype == "f16":
@@ -156,4 +187,4 @@ def from_f32(x: np.ndarray, dtype: str) -> np.ndarray:
 
 
 STORAGE = {"f16": np.float16, "bf16": np.uint16, "e4m3": np.uint8, "e5m2": np.uint8, "i8": np.int8, "i32": np.int32,
-           "f32": np.float32}
+           "f32": np.float32, "mxe4m3": np.uint8, "mxe5m2": np.uint8}

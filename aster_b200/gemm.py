@@ -18,7 +18,8 @@ from .dtypes import STORAGE
 from .execution import GpuBuffer
 
 DTYPE_CODES = {"f16": nat.F16, "bf16": nat.BF16, "e4m3": nat.E4M3, "f32": nat.F32, "e5m2": nat.E5M2, "i8": nat.I8,
-               "i32": nat.I32, "e5m2_e4m3": nat.E5M2_E4M3, "e4m3_e5m2": nat.E4M3_E5M2}
+               "i32": nat.I32, "e5m2_e4m3": nat.E5M2_E4M3, "e4m3_e5m2": nat.E4M3_E5M2, "mxe4m3": nat.MXE4M3,
+               "mxe5m2": nat.MXE5M2}
 B_LAYOUT_CODES = {"row_major": nat.B_ROW_MAJOR_NK, "ref_preshuffled": nat.B_REF_PRESHUFFLED, "packed": nat.B_PACKED}
 EPILOGUE_CODES = {"none": nat.EPI_NONE, "bias_relu": nat.EPI_BIAS_RELU, "bias": nat.EPI_BIAS, "relu": nat.EPI_RELU}
 BIAS_AXIS_CODES = {"n": nat.BIAS_AXIS_N, "m": nat.BIAS_AXIS_M}
@@ -124,6 +125,11 @@ class GemmPlan:
     def pack_b(self, b_in, b_packed, stream=None) -> None:
         nat.call("b200_pack_b", self.handle, _ptr(b_in), _ptr(b_packed), _ptr(stream))
 
+    def set_mx_scales(self, scales_a_packed, scales_b_packed) -> None:
+        """Attach the packed E8M0 scales of A and B (device addresses, see
+        :func:`pack_mx_scales`) to a block-scaled plan; they must outlive its launches."""
+        nat.call("b200_gemm_plan_set_mx_scales", self.handle, _ptr(scales_a_packed), _ptr(scales_b_packed))
+
     def run(self, A, B, Cbuf, bias=None, scale_a=None, scale_b=None, workspace=None, workspace_bytes=0, stream=None) -> None:
         """Enqueue one launch.  All pointers are device addresses (GpuBuffer, int or c_void_p)."""
         if isinstance(workspace, GpuBuffer) and not workspace_bytes:
@@ -184,6 +190,18 @@ def gemm_splitk_noalloc(A, B, Cbuf, M: int, N: int, K: int, dtype_ab: str = "bf1
              DTYPE_CODES[dtype_c], int(split_k), _ptr(stream))
 
 
+def mx_scales_bytes(rows: int, K: int) -> int:
+    """Bytes of the packed scale array for ``rows`` rows of ``K`` block-scaled elements."""
+    n = C.c_size_t(0)
+    nat.call("b200_mx_scales_bytes", int(rows), int(K), C.byref(n))
+    return n.value
+
+
+def pack_mx_scales(scales_in, scales_packed, rows: int, K: int, stream=None) -> None:
+    """Device-side reorder of row-major scales ``[rows][K/32]`` into the kernel's streaming order."""
+    nat.call("b200_pack_mx_scales", _ptr(scales_in), _ptr(scales_packed), int(rows), int(K), _ptr(stream))
+
+
 def _check_operand(name: str, arr: np.ndarray, shape, dtype: str) -> np.ndarray:
     want = STORAGE[dtype]
     if not isinstance(arr, np.ndarray):
@@ -210,6 +228,8 @@ def gemm(
     plan: Optional[GemmPlan] = None,
     b_layout: str = "row_major",
     tail_split: bool = False,
+    block_scales_a: Optional[np.ndarray] = None,
+    block_scales_b: Optional[np.ndarray] = None,
     **plan_kw,
 ) -> np.ndarray:
     """``C = epilogue(A . B^T)`` on the GPU with host arrays in and a host array out.
@@ -219,6 +239,8 @@ def gemm(
     layout ("ref_preshuffled" or "packed" = row-major to be packed) is packed on the device
     first.  ``tail_split=True`` lends the plan its optional workspace so that a mostly idle
     last round of tiles is cut along K (changes the fp32 summation order of those tiles).
+    For the block-scaled types ("mxe4m3", "mxe5m2") ``block_scales_a`` / ``block_scales_b`` are
+    the E8M0 scale bytes ``[M, K/32]`` / ``[N, K/32]`` (see :func:`aster_b200.dtypes.quantize_mx`).
     Returns ``[M, N]`` float32, bf16 bit patterns (uint16) for ``dtype_c="bf16"``, or the int32
     sums for int8 inputs with ``dtype_c="i32"``.
     """
@@ -252,6 +274,19 @@ def gemm(
             bufs.append(packed)
             plan.pack_b(dB, packed)
             dB = packed
+        if dtype_ab.startswith("mx"):
+            if block_scales_a is None or block_scales_b is None:
+                raise ValueError(f"{dtype_ab} needs block_scales_a and block_scales_b")
+            packed_scales = []
+            for name, sc, rows in (("block_scales_a", block_scales_a, M), ("block_scales_b", block_scales_b, N)):
+                sc = _check_operand(name, sc, (rows, K // 32), "e4m3")  # stored as uint8, one per 32 elements
+                out_buf = GpuBuffer(mx_scales_bytes(rows, K))
+                bufs.append(out_buf)
+                pack_mx_scales(dev(sc), out_buf, rows, K)
+                packed_scales.append(out_buf)
+            plan.set_mx_scales(*packed_scales)
+        elif block_scales_a is not None or block_scales_b is not None:
+            raise ValueError(f"block scales given for dtype_ab={dtype_ab!r}, which is not block-scaled")
         dbias = dev(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
         dsa = dev(np.array([scale_a], dtype=np.float32)) if scale_a is not None else None
         dsb = dev(np.array([scale_b], dtype=np.float32)) if scale_b is not None else None

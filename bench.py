@@ -49,6 +49,8 @@ WORKLOADS = {
                                  text="bf16 GEMM [8192,2048].[8192,2048]^T + bias N(0,0.1), ReLU, bf16 out, N(0,1) seed 2"),
     "fp8_8192": dict(M=8192, N=8192, K=8192, dtype_ab="e4m3", dtype_c="bf16", dist="normal", seed=3,
                      text="fp8-e4m3 GEMM M=N=K=8192, per-tensor scales amax/448, N(0,1) seed 3, bf16 out"),
+    "int8_8192": dict(M=8192, N=8192, K=8192, dtype_ab="i8", dtype_c="i32", dist="int8", seed=7,
+                      text="int8 GEMM M=N=K=8192, integers in [-128,127] seed 7, exact int32 sums out (TFLOP/s reads as TOP/s)"),
     "sharded_65536": dict(M=65536, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, strong=True,
                           text="bf16 GEMM M=65536 N=K=8192 split by M rows over the GPUs, U(-1,1) seed 4"),
     "decode_16": dict(M=16, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True,
@@ -77,9 +79,14 @@ def measured_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "_source": "fallback"}
 
 
+EIGHT_BIT = ("e4m3", "e5m2", "i8")  # operand types that run at twice the 16-bit tensor rate
+
+
 def draw(rng, shape, dist):
     if dist == "uniform":
         return rng.uniform(-1.0, 1.0, size=shape).astype(np.float32)
+    if dist == "int8":
+        return rng.integers(-128, 128, size=shape).astype(np.float32)
     return rng.standard_normal(size=shape).astype(np.float32)
 
 
@@ -479,11 +486,11 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
         achieved = flops_per_gpu / (ms_per_step * 1e-3) / 1e12
         sustained = ms_total > 1000.0
         peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
-        if w["dtype_ab"] == "e4m3":
-            peak *= 2.0  # no measured fp8 figure: twice the measured bf16 cuBLAS rate
+        if w["dtype_ab"] in EIGHT_BIT:
+            peak *= 2.0  # no measured 8-bit figure: twice the measured bf16 cuBLAS rate
         unit, bound = "TFLOP/s", "tensor"
-        peak_kind = ("sustained" if sustained else "burst") + (" bf16 x2 for fp8" if w["dtype_ab"] == "e4m3" else " bf16")
-    nominal = 4500.0 if w["dtype_ab"] == "e4m3" else 2250.0
+        peak_kind = ("sustained" if sustained else "burst") + (" bf16 x2 for 8-bit inputs" if w["dtype_ab"] in EIGHT_BIT else " bf16")
+    nominal = 4500.0 if w["dtype_ab"] in EIGHT_BIT else 2250.0
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if w.get("strong") else "weak",

@@ -107,7 +107,14 @@ enum {
   B200_I8 = 5,        /* signed 8-bit integers, 32-bit integer accumulation                    */
   B200_I32 = 6,       /* dtype_c only, with B200_I8 inputs: the integer sums, unchanged        */
   B200_E5M2_E4M3 = 7, /* A e5m2, B e4m3                                                        */
-  B200_E4M3_E5M2 = 8  /* A e4m3, B e5m2                                                        */
+  B200_E4M3_E5M2 = 8, /* A e4m3, B e5m2                                                        */
+  /* Block-scaled fp8 ("MX"): every 32 consecutive elements of a row of A or B along K share
+   * one E8M0 scale (a power of two, stored as the biased exponent byte; 127 = 1.0), applied
+   * inside the tensor core.  The B200 form of the reference's v_mfma_scale_f32_16x16x128_f8f6f4
+   * (include/aster/Dialect/AMDGCN/IR/Instructions/MMA.td; test/integration/
+   * test_mfma_f8f6f4_e2e.py:39-95).  Scales are attached with b200_gemm_plan_set_mx_scales. */
+  B200_MXE4M3 = 9,
+  B200_MXE5M2 = 10
 };
 /* Layout of the B operand handed to b200_pack_b / b200_gemm_run. */
 enum {
@@ -238,6 +245,18 @@ int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, 
                             int num_ctas, void* stream);
 /* out[i] = max(a[i] + b[i], 0); examples/07_simple_fusion/simple_fusion.py:62-144. */
 int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void* stream);
+
+/* ---- block-scaled fp8 (dtype_ab = B200_MXE4M3 | B200_MXE5M2) -----------------------------
+ * C = (A * 2^(sa-127)) . (B * 2^(sb-127))^T with sa[M][K/32], sb[N][K/32] bytes.  K % 32 == 0;
+ * row-major B; cta_group 1; tile_n 128.  The kernel streams the scales in blocks of
+ * [128 rows][4 K blocks]; b200_pack_mx_scales turns row-major scales (device memory,
+ * [rows][K/32] bytes) into that order (device memory of b200_mx_scales_bytes bytes, 16-byte
+ * aligned).  b200_gemm_plan_set_mx_scales attaches the packed scales of A and B to a plan;
+ * b200_gemm_run / _time then run it like any other plan (scale_a / scale_b stay available as
+ * per-tensor factors). */
+int b200_mx_scales_bytes(int64_t rows, int64_t K, size_t* bytes);
+int b200_pack_mx_scales(const void* scales_in, void* scales_packed, int64_t rows, int64_t K, void* stream);
+int b200_gemm_plan_set_mx_scales(b200_gemm_plan* plan, const void* scales_a_packed, const void* scales_b_packed);
 
 /* ---- optional: gather row shards of C onto every GPU (NCCL over NVLink) ------------------
  * No counterpart in the reference, whose multi-GPU support is fan-out of whole configurations

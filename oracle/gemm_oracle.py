@@ -130,6 +130,10 @@ def decode(arr: np.ndarray, dtype: str) -> np.ndarray:
 def encode(x: np.ndarray, dtype: str) -> np.ndarray:
     if dtype == "e5m2":
         return e5m2_encode(x)
+    if dtype == "i32":
+        return np.rint(np.asarray(x, dtype=np.float64)).astype(np.int32)
+    if dtype == "i8":
+        return np.clip(np.rint(np.asarray(x, dtype=np.float64)), -128, 127).astype(np.int8)
     if dtype == "f16":
         return np.asarray(x, dtype=np.float32).astype(np.float16)
     if dtype == "bf16":
@@ -161,6 +165,41 @@ def gemm_f32(A: np.ndarray, B: np.ndarray, dtype_ab: str = "f16") -> np.ndarray:
     """
     ta, tb = operand_types(dtype_ab)
     return decode(A, ta) @ decode(B, tb).T
+
+
+def mx_quantize(x: np.ndarray, elem: str = "e4m3"):
+    """OCP microscaling quantisation along K in blocks of 32: shared exponent
+    ``floor(log2(amax)) - emax_elem`` as an E8M0 byte (bias 127), elements rounded to nearest even
+    with saturation.  Written block by block, independently of the product's vectorised version.
+    Returns (bits, scales) as uint8 arrays ``[rows, K]`` and ``[rows, K/32]``."""
+    emax = {"e4m3": 8, "e5m2": 15}[elem]
+    x = np.asarray(x, dtype=np.float32)
+    rows, K = x.shape
+    bits = np.empty((rows, K), dtype=np.uint8)
+    scales = np.empty((rows, K // 32), dtype=np.uint8)
+    for kb in range(K // 32):
+        blk = x[:, 32 * kb: 32 * kb + 32]
+        amax = np.abs(blk).max(axis=1)
+        safe = np.where(amax > 0, amax, 1.0)
+        shared = np.where(amax > 0, np.floor(np.log2(safe.astype(np.float64))).astype(np.int64) - emax, 0)
+        shared = np.clip(shared, -127, 127)
+        scales[:, kb] = (shared + 127).astype(np.uint8)
+        bits[:, 32 * kb: 32 * kb + 32] = encode((blk.astype(np.float64) / np.exp2(shared.astype(np.float64))[:, None]).astype(np.float32), elem)
+    return bits, scales
+
+
+def mx_dequantize(bits: np.ndarray, scales: np.ndarray, elem: str = "e4m3") -> np.ndarray:
+    """float64 values ``element * 2**(scale - 127)`` of block-scaled data."""
+    vals = decode(bits, elem).astype(np.float64)
+    factor = np.exp2(np.asarray(scales, dtype=np.float64) - 127.0)
+    return vals * np.repeat(factor, 32, axis=1)
+
+
+def gemm_mx(A, B, scales_a, scales_b, elem: str = "e4m3") -> np.ndarray:
+    """Block-scaled product in float64, returned as float32: what v_mfma_scale_f32_*_f8f6f4
+    computes per 32-element block with E8M0 scales (test/integration/test_mfma_f8f6f4_e2e.py:39-95),
+    summed over K."""
+    return (mx_dequantize(A, scales_a, elem) @ mx_dequantize(B, scales_b, elem).T).astype(np.float32)
 
 
 def gemm_i32(A: np.ndarray, B: np.ndarray) -> np.ndarray:

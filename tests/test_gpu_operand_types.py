@@ -121,3 +121,87 @@ def test_int8_through_the_operator_surface(gpu, tmp_path):
     a, b = int8_inputs(384, 256, 512, seed=3)
     c, times = execute_multitile_hsaco(cfg, path, 3, a, b, skip_gpu_check=True)
     assert len(times) == 3 and c.dtype == np.int32 and np.array_equal(c.reshape(384, 256), orc.gemm_i32(a, b))
+
+
+def mx_inputs(M, N, K, seed, elem="e4m3", spread=True):
+    """Random operands whose 32-element blocks differ in magnitude by orders, so that the block
+    scales matter; quantised by the oracle's own block-by-block routine."""
+    rng = np.random.default_rng(seed)
+
+    def draw(rows):
+        x = rng.standard_normal((rows, K)).astype(np.float32)
+        if spread:
+            x *= np.repeat(np.exp2(rng.integers(-12, 13, (rows, K // 32))).astype(np.float32), 32, axis=1)
+        return x
+
+    a, b = draw(M), draw(N)
+    (qa, sa), (qb, sb) = orc.mx_quantize(a, elem), orc.mx_quantize(b, elem)
+    return a, b, qa, sa, qb, sb
+
+
+class TestBlockScaledFp8:
+    """E8M0 scales per 32 elements of K, applied inside the tensor core (the reference's
+    v_mfma_scale_f32_16x16x128_f8f6f4 tests, test/integration/test_mfma_f8f6f4_e2e.py:39-95)."""
+
+    def test_known_answers(self, gpu):
+        # 1.75 x 1.25 over K = 128 with scales 4 and 2 -> 1.75 * 1.25 * 128 * 8 = 2240
+        M = N = 16
+        a = from_f32(np.full((M, 128), 1.75, np.float32), "e4m3")
+        b = from_f32(np.full((N, 128), 1.25, np.float32), "e4m3")
+        sa, sb = np.full((M, 4), 129, np.uint8), np.full((N, 4), 128, np.uint8)
+        got = gemm(a, b, dtype_ab="mxe4m3", dtype_c="f32", block_scales_a=sa, block_scales_b=sb)
+        assert np.array_equal(got, np.full((M, N), 2240.0, np.float32))
+        # two halves of K with different scales: 64 * (1 * 1) * 2 + 64 * (1.5 * 1) * 0.5 = 176
+        a = from_f32(np.concatenate([np.full((M, 64), 1.0), np.full((M, 64), 1.5)], axis=1).astype(np.float32), "e4m3")
+        b = from_f32(np.ones((N, 128), np.float32), "e4m3")
+        sa = np.repeat(np.uint8([[128, 128, 126, 126]]), M, axis=0)
+        sb = np.full((N, 4), 127, np.uint8)
+        got = gemm(a, b, dtype_ab="mxe4m3", dtype_c="f32", block_scales_a=sa, block_scales_b=sb)
+        assert np.array_equal(got, np.full((M, N), 176.0, np.float32))
+
+    def test_each_row_and_block_uses_its_own_scale(self, gpu):
+        # ones everywhere; scales chosen so that C[m, n] = sum_kb 2^(ea[m, kb] + eb[n, kb]) * 32 is distinct per (m, n)
+        M, N, K = 256, 128, 256
+        rng = np.random.default_rng(1)
+        sa = rng.integers(124, 131, (M, K // 32)).astype(np.uint8)  # sums stay within 24 significant bits
+        sb = rng.integers(124, 131, (N, K // 32)).astype(np.uint8)
+        ones = from_f32(np.ones((max(M, N), K), np.float32), "e4m3")
+        got = gemm(ones[:M], ones[:N], dtype_ab="mxe4m3", dtype_c="f32", block_scales_a=sa, block_scales_b=sb)
+        want = 32.0 * (np.exp2(sa.astype(np.float64) - 127) @ np.exp2(sb.astype(np.float64) - 127).T)
+        assert np.array_equal(got, want.astype(np.float32))  # powers of two: exact
+
+    @pytest.mark.parametrize("elem", ["e4m3", "e5m2"])
+    @pytest.mark.parametrize("shape", [(128, 128, 128), (256, 384, 1024), (200, 136, 160), (1000, 520, 2080), (512, 512, 8192)])
+    def test_against_oracle(self, gpu, elem, shape):
+        M, N, K = shape
+        a, b, qa, sa, qb, sb = mx_inputs(M, N, K, seed=M + K, elem=elem)
+        want = orc.gemm_mx(qa, qb, sa, sb, elem)
+        for dtype_c in ("f32", "bf16"):
+            got = gemm(qa, qb, dtype_ab="mx" + elem, dtype_c=dtype_c, block_scales_a=sa, block_scales_b=sb)
+            want_c = orc.decode(orc.encode(want, dtype_c), dtype_c)
+            assert orc.rel_frobenius(orc.decode(got, dtype_c), want_c) <= 1e-3
+        # against the unquantised product the error is the quantisation noise of the format
+        noise = orc.rel_frobenius(orc.gemm_mx(qa, qb, sa, sb, elem), a.astype(np.float64) @ b.astype(np.float64).T)
+        assert noise < (0.08 if elem == "e4m3" else 0.16)
+
+    def test_epilogue_split_k_and_tail_split(self, gpu):
+        M, N, K = 384, 256, 2048
+        _, _, qa, sa, qb, sb = mx_inputs(M, N, K, seed=4, spread=False)
+        bias = np.random.default_rng(5).standard_normal(N).astype(np.float32)
+        want = np.maximum(orc.gemm_mx(qa, qb, sa, sb) + bias[None, :], 0)
+        kw = dict(dtype_ab="mxe4m3", dtype_c="f32", block_scales_a=sa, block_scales_b=sb, bias=bias, relu=True)
+        for extra in ({}, {"split_k": 3}, {"max_ctas": 4, "tail_split": True}, {"stages": 2}):
+            assert orc.rel_frobenius(gemm(qa, qb, **kw, **extra), want) <= 1e-3, extra
+
+    def test_refusals(self, gpu):
+        with pytest.raises(nat.B200Error, match="K %% 32 == 0|K % 32 == 0"):
+            GemmPlan(128, 128, 144, "mxe4m3", "f32")
+        with pytest.raises(nat.B200Error, match="cta_group=1"):
+            GemmPlan(256, 128, 128, "mxe4m3", "f32", cta_group=2)
+        with pytest.raises(nat.B200Error, match="tile_n=128"):
+            GemmPlan(256, 256, 128, "mxe4m3", "f32", tile_n=256)
+        with pytest.raises(nat.B200Error, match="not block-scaled"):
+            GemmPlan(128, 128, 128, "e4m3", "f32").set_mx_scales(16, 16)
+        plan = GemmPlan(128, 128, 128, "mxe4m3", "f32")
+        with pytest.raises(nat.B200Error, match="needs its scales first"):
+            plan.run(1024, 2048, 4096)
