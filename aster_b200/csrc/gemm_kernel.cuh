@@ -363,8 +363,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr uint32_t kBBytes = kBRows * kRowBytes;
   constexpr uint32_t kStageBytes = stage_bytes(BN, CG, MX);
   constexpr uint32_t kTmemCols = tmem_columns(BN, MX);
-  static_assert(!MX || (CG == 1 && BN == 128), "block-scaled tiles: one CTA, 128 columns");
-  static_assert(!MX || 2 * BN + 2 * kScaleTmemCols <= 512, "accumulators and scales share the 512 columns");
+  // Block-scaled tiles of 256 columns keep a single accumulator: two of them would fill the
+  // 512 TMEM columns and leave none for the scales (the epilogue then does not overlap the next
+  // main loop, which costs less than the shared-memory bound of a 128-column tile).
+  constexpr int kAccBufs = (MX && BN == 256) ? 1 : 2;
+  static_assert(!MX || (CG == 1 && (BN == 128 || BN == 256)), "block-scaled tiles: one CTA, 128 or 256 columns");
+  static_assert(!MX || kAccBufs * BN + 2 * kScaleTmemCols <= 512, "accumulators and scales share the 512 columns");
   constexpr int kTileM = kBM * CG;
 
   extern __shared__ uint8_t smem_raw[];
@@ -537,21 +541,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               // Scales of this stage: shared memory -> TMEM (alternating column sets), then the
               // four block-scaled MMAs; tcgen05 operations of one thread execute in order.
               const uint32_t sf_smem = smem_base + static_cast<uint32_t>(stage) * kStageBytes + kABytes + kBBytes;
-              const uint32_t sf_tmem = tmem_base + 2u * BN + sf_set * kScaleTmemCols;  // behind the two accumulators
-              if (do_mma) {
-                tmem_cp_32x128b_warpx4(sf_tmem, make_smem_desc_scales(sf_smem));
-#pragma unroll
-                for (int q = 0; q < BN / 128; ++q) {
-                  tmem_cp_32x128b_warpx4(sf_tmem + 4u + 4u * q, make_smem_desc_scales(sf_smem + (1 + q) * kScaleBlockBytes));
-                }
-                const uint64_t da = (static_cast<uint64_t>(desc_hi) << 32) | a_lo;
-                const uint64_t db = (static_cast<uint64_t>(desc_hi) << 32) | (a_lo + b_off);
-#pragma unroll
-                for (uint32_t j = 0; j < kMmasPerStage; ++j) {
-                  umma_mx_ss(tmem_d, da + 2u * j, db + 2u * j, idesc_mx_with_scale_id(idesc, j), (kb != 0 || j != 0) ? 1u : 0u, sf_tmem,
-                             sf_tmem + 4u);
-                }
-              }
+              const uint32_t sf_tmem = tmem_base + static_cast<uint32_t>(kAccBufs * BN) + sf_set * kScaleTmemCols;  // behind the accumulators
+              if (do_mma) umma_mx_stage<BN / 128>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, sf_tmem, smem_desc_lo_scales(sf_smem));
             } else {
               if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, mma_kind);
             }
@@ -578,7 +569,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if constexpr (CG == 2) umma_commit<CG>(acc_full_bar(acc) + peer_delta);
         }
         __syncwarp();
-        acc ^= 1;
+        acc = (acc + 1) % kAccBufs;
         if (acc == 0) acc_phase ^= 1u;
       }
       if (!ok) {
@@ -753,7 +744,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           mbar_arrive_remote(map_to_cta(acc_empty_bar(acc), 0u));
         }
       }
-      acc ^= 1;
+      acc = (acc + 1) % kAccBufs;
       if (acc == 0) acc_phase ^= 1u;
     }
   }

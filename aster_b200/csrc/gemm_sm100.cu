@@ -83,7 +83,10 @@ KernelFn select_kernel_cg(int bn, bool f32) {
 
 KernelFn select_kernel(int bn, int dtype_c, int cta_group, bool mx) {
   const bool f32 = dtype_c == B200_F32 || dtype_c == B200_I32;  // 32-bit outputs share the store path
-  if (mx) return f32 ? gemm::gemm_tn_kernel<128, float, 1, true> : gemm::gemm_tn_kernel<128, __nv_bfloat16, 1, true>;
+  if (mx) {
+    if (bn == 256) return f32 ? gemm::gemm_tn_kernel<256, float, 1, true> : gemm::gemm_tn_kernel<256, __nv_bfloat16, 1, true>;
+    return f32 ? gemm::gemm_tn_kernel<128, float, 1, true> : gemm::gemm_tn_kernel<128, __nv_bfloat16, 1, true>;
+  }
   return cta_group == 2 ? select_kernel_cg<2>(bn, f32) : select_kernel_cg<1>(bn, f32);
 }
 
@@ -499,7 +502,7 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
     B200_REQUIRE(d.K % 32 == 0, "gemm_plan_create: block-scaled inputs need K %% 32 == 0 (one scale per 32 elements), got K=%lld", (long long)d.K);
     B200_REQUIRE(d.b_layout == B200_B_ROW_MAJOR_NK, "gemm_plan_create: block-scaled inputs take row-major B");
     B200_REQUIRE(d.cta_group <= 1 && d.tile_m != 2 * gemm::kBM, "gemm_plan_create: block-scaled inputs run with cta_group=1");
-    B200_REQUIRE(d.tile_n == 0 || d.tile_n == 128, "gemm_plan_create: block-scaled inputs use tile_n=128 (got %d)", d.tile_n);
+    B200_REQUIRE(d.tile_n == 0 || d.tile_n == 128 || d.tile_n == 256, "gemm_plan_create: block-scaled inputs use tile_n=128 or 256 (got %d)", d.tile_n);
   }
   B200_REQUIRE(d.dtype_c == B200_F32 || d.dtype_c == B200_BF16 || d.dtype_c == B200_I32,
                "gemm_plan_create: dtype_c=%d is not f32, bf16 or i32", d.dtype_c);
@@ -555,7 +558,11 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
 
   // Tile width: the widest tile whose tile count still fills the machine; wide tiles halve the
   // shared-memory traffic per flop, narrow ones keep more SMs busy on small problems.
-  int bn = mx ? 128 : d.tile_n;
+  int bn = d.tile_n;
+  if (bn == 0 && mx) {
+    // 256 columns unless that leaves SMs without a tile: a 128-column tile is bound by shared-memory reads.
+    bn = (static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, 256) >= kDefaultSms) ? 256 : 128;
+  }
   if (bn == 0) {
     const int units = kDefaultSms / cg;  // CTAs or pairs that run at once
     bn = 256;

@@ -51,6 +51,9 @@ WORKLOADS = {
                      text="fp8-e4m3 GEMM M=N=K=8192, per-tensor scales amax/448, N(0,1) seed 3, bf16 out"),
     "int8_8192": dict(M=8192, N=8192, K=8192, dtype_ab="i8", dtype_c="i32", dist="int8", seed=7,
                       text="int8 GEMM M=N=K=8192, integers in [-128,127] seed 7, exact int32 sums out (TFLOP/s reads as TOP/s)"),
+    "mxfp8_8192": dict(M=8192, N=8192, K=8192, dtype_ab="mxe4m3", dtype_c="bf16", dist="normal", seed=8,
+                       text="block-scaled fp8 GEMM M=N=K=8192 (e4m3 elements, one E8M0 scale per 32 elements of K, scales resident "
+                            "on the device), N(0,1) seed 8, bf16 out"),
     "sharded_65536": dict(M=65536, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, strong=True,
                           text="bf16 GEMM M=65536 N=K=8192 split by M rows over the GPUs, U(-1,1) seed 4"),
     "decode_16": dict(M=16, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True,
@@ -79,7 +82,16 @@ def measured_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "_source": "fallback"}
 
 
-EIGHT_BIT = ("e4m3", "e5m2", "i8")  # operand types that run at twice the 16-bit tensor rate
+EIGHT_BIT = ("e4m3", "e5m2", "i8", "mxe4m3", "mxe5m2")  # operand types that run at twice the 16-bit tensor rate
+
+
+def operands_f32(ops: dict, dtype_ab: str):
+    """float32 values of the stored operands (block scales applied)."""
+    from aster_b200.dtypes import dequantize_mx, to_f32
+
+    if dtype_ab.startswith("mx"):
+        return (dequantize_mx(ops["A"], ops["block_scales_a"], dtype_ab[2:]), dequantize_mx(ops["B"], ops["block_scales_b"], dtype_ab[2:]))
+    return to_f32(ops["A"], dtype_ab), to_f32(ops["B"], dtype_ab)
 
 
 def draw(rng, shape, dist):
@@ -92,7 +104,7 @@ def draw(rng, shape, dist):
 
 def host_operands(w: dict, rank: int, rows: int):
     """Seeded synthetic A (this rank's rows), B, bias and scales in storage form."""
-    from aster_b200.dtypes import from_f32, quantize_e4m3
+    from aster_b200.dtypes import from_f32, quantize_e4m3, quantize_mx
     from aster_b200.sharding import sharded_uniform_rows
 
     seed = w["seed"]
@@ -104,8 +116,11 @@ def host_operands(w: dict, rank: int, rows: int):
     else:
         a = draw(np.random.default_rng([seed, rank]), (rows, w["K"]), w["dist"])
     b = draw(np.random.default_rng(seed + 1), (w["N"], w["K"]), w["dist"])
-    out = dict(scale_a=None, scale_b=None, bias=None)
-    if w["dtype_ab"] == "e4m3":
+    out = dict(scale_a=None, scale_b=None, bias=None, block_scales_a=None, block_scales_b=None)
+    if w["dtype_ab"].startswith("mx"):
+        out["A"], out["block_scales_a"] = quantize_mx(a, w["dtype_ab"][2:])
+        out["B"], out["block_scales_b"] = quantize_mx(b, w["dtype_ab"][2:])
+    elif w["dtype_ab"] == "e4m3":
         out["A"], sa = quantize_e4m3(a)
         out["B"], sb = quantize_e4m3(b)
         out["scale_a"], out["scale_b"] = float(sa), float(sb)
@@ -257,8 +272,7 @@ def cpu_gemm_seconds(w: dict, rows: int, max_seconds: float, max_reps: int):
     use_all_host_threads()
     rows = min(rows, w["M"])
     ops = host_operands(w, 0, rows)
-    a32 = orc.decode(ops["A"], w["dtype_ab"])
-    b32 = orc.decode(ops["B"], w["dtype_ab"])
+    a32, b32 = operands_f32(ops, w["dtype_ab"])
     alpha = 1.0 if ops["scale_a"] is None else float(np.float32(ops["scale_a"]) * np.float32(ops["scale_b"]))
     best, reps, t_start = float("inf"), 0, time.perf_counter()
     while reps < max_reps and (reps == 0 or time.perf_counter() - t_start < max_seconds):
@@ -309,7 +323,7 @@ def run_reference_arm(args, w: dict, name: str) -> dict:
     from oracle import gemm_oracle as orc
 
     ops = host_operands(w, 0, rows)
-    a32, b32 = orc.decode(ops["A"], w["dtype_ab"]), orc.decode(ops["B"], w["dtype_ab"])
+    a32, b32 = operands_f32(ops, w["dtype_ab"])
     alpha = 1.0 if ops["scale_a"] is None else float(np.float32(ops["scale_a"]) * np.float32(ops["scale_b"]))
 
     def step():
@@ -422,6 +436,17 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
             small[key].copy_from_host(arr)
     ws_bytes = res.workspace_bytes or res.optional_workspace_bytes
     ws = GpuBuffer(ws_bytes) if ws_bytes else None
+    if ops["block_scales_a"] is not None:
+        from aster_b200.gemm import mx_scales_bytes, pack_mx_scales
+
+        for key, n_rows in (("block_scales_a", rows), ("block_scales_b", N)):
+            raw = GpuBuffer(ops[key].nbytes)
+            raw.copy_from_host(ops[key])
+            small[key] = GpuBuffer(mx_scales_bytes(n_rows, K))
+            pack_mx_scales(raw, small[key], n_rows, K)
+            nat.call("b200_device_synchronize")
+            raw.free()
+        plan.set_mx_scales(small["block_scales_a"], small["block_scales_b"])
 
     def run_step(i):
         dA, dB, dC = sets[i % n_sets]
@@ -439,7 +464,9 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
     out = np.empty((rows, N), dtype=STORAGE[w["dtype_c"]])
     sets[(args.warmup + args.steps - 1) % n_sets][2].copy_to_host(out)
     pick = np.sort(np.random.default_rng(0).choice(rows, min(rows, 64), replace=False))
-    acc = to_f32(ops["A"][pick], w["dtype_ab"]) @ to_f32(ops["B"], w["dtype_ab"]).T
+    a32, b32 = operands_f32(dict(ops, A=ops["A"][pick], block_scales_a=None if ops["block_scales_a"] is None else ops["block_scales_a"][pick]),
+                            w["dtype_ab"])
+    acc = a32 @ b32.T
     if ops["scale_a"] is not None:
         acc = acc * np.float32(np.float32(ops["scale_a"]) * np.float32(ops["scale_b"]))
     if ops["bias"] is not None:
