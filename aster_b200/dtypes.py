@@ -187,4 +187,4 @@ def from_f32(x: np.ndarray, dtype: str) -> np.ndarray:
 
 
 STORAGE = {"f16": np.float16, "bf16": np.uint16, "e4m3": np.uint8, "e5m2": np.uint8, "i8": np.int8, "i32": np.int32,
-           "f32": np.float32, "mxe4m3": np.uint8, "mxe5m2": np.uint8}
+           "f32": np.float32, "mxe4m3": np.uint8, "mxe5m2": np.uint8, "e5m2_e4m3": np.uint8, "e4m3_e5m2": np.uint8}
