@@ -74,11 +74,10 @@ struct Params {
   const float* scale_a;
   const float* scale_b;
   void* C;
-  // Block-scaled kernels: E8M0 scales of A and B in blocks of [128 rows][4 K blocks] (row r of a
-  // block at byte (r % 32) * 16 + (r / 32) * 4), ordered [row block][K stage]; sf_k_stages =
-  // ceil(K / 128) blocks per row block.
-  const uint8_t* sfa;
-  const uint8_t* sfb;
+  // Block-scaled kernels: the E8M0 scales of A and B come in blocks of [128 rows][4 K blocks]
+  // (row r of a block at byte (r % 32) * 16 + (r / 32) * 4), ordered [row block][K stage] with
+  // sf_k_stages = ceil(K / 128) blocks per row block; the kernel's two scale tensor maps see
+  // each array as one 512-byte row per block.
   int sf_k_stages;
   const void* b_packed;  // non-null: B comes as packed tile images, streamed with 1-D bulk copies
   float* workspace;      // split-K partial sums [split][M][N] fp32
@@ -353,7 +352,8 @@ __device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], boo
 // commits arrive on each; acc_empty[] lives in the leader and collects both CTAs' epilogues.
 template <int BN, typename OutT, int CG, bool MX = false>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const Params p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
   using namespace sm100;
   static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
@@ -362,12 +362,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr uint32_t kABytes = kBM * kRowBytes;
   constexpr uint32_t kBBytes = kBRows * kRowBytes;
   constexpr uint32_t kStageBytes = stage_bytes(BN, CG, MX);
+  constexpr uint32_t kLoadBytes = kABytes + kBBytes + (MX ? kScaleBlockBytes * (1 + BN / 128) : 0);  // bytes one CTA copies per stage
   constexpr uint32_t kTmemCols = tmem_columns(BN, MX);
   // Block-scaled tiles of 256 columns keep a single accumulator: two of them would fill the
   // 512 TMEM columns and leave none for the scales (the epilogue then does not overlap the next
   // main loop, which costs less than the shared-memory bound of a 128-column tile).
   constexpr int kAccBufs = (MX && BN == 256) ? 1 : 2;
-  static_assert(!MX || (CG == 1 && (BN == 128 || BN == 256)), "block-scaled tiles: one CTA, 128 or 256 columns");
+  static_assert(!MX || BN == 128 || BN == 256, "block-scaled tiles are 128 or 256 columns wide");
   static_assert(!MX || kAccBufs * BN + 2 * kScaleTmemCols <= 512, "accumulators and scales share the 512 columns");
   constexpr int kTileM = kBM * CG;
 
@@ -415,6 +416,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     fence_proxy_async_smem();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if constexpr (MX) {
+      prefetch_tensormap(&tmap_sfa);
+      prefetch_tensormap(&tmap_sfb);
+    }
   }
   if (warp == 1) tmem_alloc<CG>(tmem_slot, kTmemCols);
   tc_fence_before_sync();
@@ -447,22 +452,24 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const int k_elem = (kb0 + kb) * p.kb_elems;
+          // Block-scaled stages: scale blocks behind the operand tiles.  Every CTA takes the block
+          // of its own 128 rows of A and the blocks of all BN columns of B.  K stages beyond the
+          // data (split-K padding) carry zero-filled operands, so any scale will do there.
+          [[maybe_unused]] const uint32_t sf_dst = b_dst + kBBytes;
+          [[maybe_unused]] const int ks = min(kb0 + kb, p.sf_k_stages - 1);
+          [[maybe_unused]] const int sfa_blk = m_blk * CG + static_cast<int>(cta_rank);
+          [[maybe_unused]] const int sfb_blk = n_blk * (BN / 128);
           if (p.debug_mode & 8) {
             // injected fault: the stage is never handed over, so the consumer's wait must run out
           } else if ((p.debug_mode & 3) == 1) {
             if (leader) mbar_arrive(full_bar(stage));
           } else if constexpr (CG == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), kABytes + kBBytes + (MX ? kScaleBlockBytes * (1 + BN / 128) : 0));
+            mbar_arrive_expect_tx(full_bar(stage), kLoadBytes);
             if constexpr (MX) {
-              const uint32_t sf_dst = b_dst + kBBytes;
-              // K stages beyond the data (split-K padding) carry zero-filled operands: any scale will do.
-              const size_t ks = static_cast<size_t>(min(kb0 + kb, p.sf_k_stages - 1));
-              bulk_load_1d(sf_dst, p.sfa + (static_cast<size_t>(m_blk) * p.sf_k_stages + ks) * kScaleBlockBytes, kScaleBlockBytes, full_bar(stage));
+              tma_load_2d(sf_dst, &tmap_sfa, full_bar(stage), 0, sfa_blk * p.sf_k_stages + ks);
 #pragma unroll
               for (int q = 0; q < BN / 128; ++q) {
-                bulk_load_1d(sf_dst + (1 + q) * kScaleBlockBytes,
-                             p.sfb + (static_cast<size_t>(n_blk * (BN / 128) + q) * p.sf_k_stages + ks) * kScaleBlockBytes, kScaleBlockBytes,
-                             full_bar(stage));
+                tma_load_2d(sf_dst + (1 + q) * kScaleBlockBytes, &tmap_sfb, full_bar(stage), 0, (sfb_blk + q) * p.sf_k_stages + ks);
               }
             }
             tma_load_2d(a_dst, &tmap_a, full_bar(stage), k_elem, a_row);
@@ -476,7 +483,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // Both CTAs' copies complete on the leader's barrier, which the leader arms with
             // the byte count of the pair.
             const uint32_t leader_full = map_to_cta(full_bar(stage), 0u);
-            if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * kStageBytes);
+            if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * kLoadBytes);
+            if constexpr (MX) {
+              tma_load_2d_pair(sf_dst, &tmap_sfa, leader_full, 0, sfa_blk * p.sf_k_stages + ks);
+#pragma unroll
+              for (int q = 0; q < BN / 128; ++q) {
+                tma_load_2d_pair(sf_dst + (1 + q) * kScaleBlockBytes, &tmap_sfb, leader_full, 0, (sfb_blk + q) * p.sf_k_stages + ks);
+              }
+            }
             tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, a_row);
             tma_load_2d_pair(b_dst, &tmap_b, leader_full, k_elem, b_row);
           }
@@ -542,7 +556,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               // four block-scaled MMAs; tcgen05 operations of one thread execute in order.
               const uint32_t sf_smem = smem_base + static_cast<uint32_t>(stage) * kStageBytes + kABytes + kBBytes;
               const uint32_t sf_tmem = tmem_base + static_cast<uint32_t>(kAccBufs * BN) + sf_set * kScaleTmemCols;  // behind the accumulators
-              if (do_mma) umma_mx_stage<BN / 128>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, sf_tmem, smem_desc_lo_scales(sf_smem));
+              if (do_mma) umma_mx_stage<CG, BN / 128>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, sf_tmem, smem_desc_lo_scales(sf_smem));
             } else {
               if (do_mma) umma_stage<CG>(tmem_d, a_lo, a_lo + b_off, desc_hi, idesc, kb != 0 ? 1u : 0u, mma_kind);
             }

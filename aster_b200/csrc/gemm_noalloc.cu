@@ -138,6 +138,7 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
   if (rc != B200_OK) return rc;
 
   CUtensorMap map_a, map_b;
+  const CUtensorMap no_scales = {};  // block scales are not part of this entry point
   rc = encode_operand(&map_a, A, dtype_ab, static_cast<uint64_t>(M), static_cast<uint64_t>(K), gemm::kBM);
   if (rc != B200_OK) return rc;
   rc = encode_operand(&map_b, B, dtype_ab, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kTileN);
@@ -170,9 +171,9 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
   const int grid = items < setup->sm_count ? items : setup->sm_count;
   const int smem = gemm::smem_bytes(kTileN, kStages, 1);
   if (dtype_c == B200_F32) {
-    gemm::gemm_tn_kernel<kTileN, float, 1><<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, p);
+    gemm::gemm_tn_kernel<kTileN, float, 1><<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, no_scales, no_scales, p);
   } else {
-    gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1><<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, p);
+    gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1><<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, no_scales, no_scales, p);
   }
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());

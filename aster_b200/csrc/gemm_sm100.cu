@@ -68,7 +68,22 @@ int make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t row
   return B200_OK;
 }
 
-using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const Params);
+// Packed block scales as a matrix of 32-bit words: one 512-byte row per [128 rows][4 K blocks]
+// block, copied whole and unswizzled.
+int make_scale_map(CUtensorMap* map, const void* base, uint64_t blocks) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return b200::fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {gemm::kScaleBlockBytes / 4, blocks};
+  cuuint64_t strides[1] = {gemm::kScaleBlockBytes};
+  cuuint32_t box[2] = {gemm::kScaleBlockBytes / 4, 1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return b200::fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (%llu scale blocks)", static_cast<int>(r), (unsigned long long)blocks);
+  return B200_OK;
+}
+
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
 
 template <int CG>
 KernelFn select_kernel_cg(int bn, bool f32) {
@@ -84,6 +99,10 @@ KernelFn select_kernel_cg(int bn, bool f32) {
 KernelFn select_kernel(int bn, int dtype_c, int cta_group, bool mx) {
   const bool f32 = dtype_c == B200_F32 || dtype_c == B200_I32;  // 32-bit outputs share the store path
   if (mx) {
+    if (cta_group == 2) {
+      if (bn == 256) return f32 ? gemm::gemm_tn_kernel<256, float, 2, true> : gemm::gemm_tn_kernel<256, __nv_bfloat16, 2, true>;
+      return f32 ? gemm::gemm_tn_kernel<128, float, 2, true> : gemm::gemm_tn_kernel<128, __nv_bfloat16, 2, true>;
+    }
     if (bn == 256) return f32 ? gemm::gemm_tn_kernel<256, float, 1, true> : gemm::gemm_tn_kernel<256, __nv_bfloat16, 1, true>;
     return f32 ? gemm::gemm_tn_kernel<128, float, 1, true> : gemm::gemm_tn_kernel<128, __nv_bfloat16, 1, true>;
   }
@@ -218,8 +237,9 @@ struct b200_gemm_plan {
   int bn = 0;
   int cg = 1;         // CTAs per MMA: 1, or 2 for a CTA pair (cluster of two)
   bool mx = false;    // block-scaled 8-bit floats: scales come from b200_gemm_plan_set_mx_scales
-  const uint8_t* sfa = nullptr;
-  const uint8_t* sfb = nullptr;
+  const void* sfa = nullptr;
+  const void* sfb = nullptr;
+  CUtensorMap map_sfa = {}, map_sfb = {};  // all zero (never dereferenced) unless mx
   int stages = 0;
   int split_k = 1;
   int grid = 0;
@@ -423,8 +443,6 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.scale_a = scale_a;
   p.scale_b = scale_b;
   p.C = C;
-  p.sfa = plan->sfa;
-  p.sfb = plan->sfb;
   p.sf_k_stages = ceil_div(d.K, gemm::kRowBytes);
   p.b_packed = direct_b(plan) ? B : nullptr;
   p.workspace = static_cast<float*>(workspace);
@@ -461,9 +479,9 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200_CUDA_OK(cudaLaunchKernelEx(&cfg, plan->kernel, plan->map_a, plan->map_b, p));
+    B200_CUDA_OK(cudaLaunchKernelEx(&cfg, plan->kernel, plan->map_a, plan->map_b, plan->map_sfa, plan->map_sfb, p));
   } else {
-    plan->kernel<<<plan->grid, gemm::kThreads, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+    plan->kernel<<<plan->grid, gemm::kThreads, plan->smem, stream>>>(plan->map_a, plan->map_b, plan->map_sfa, plan->map_sfb, p);
   }
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());
@@ -501,7 +519,6 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   if (mx) {
     B200_REQUIRE(d.K % 32 == 0, "gemm_plan_create: block-scaled inputs need K %% 32 == 0 (one scale per 32 elements), got K=%lld", (long long)d.K);
     B200_REQUIRE(d.b_layout == B200_B_ROW_MAJOR_NK, "gemm_plan_create: block-scaled inputs take row-major B");
-    B200_REQUIRE(d.cta_group <= 1 && d.tile_m != 2 * gemm::kBM, "gemm_plan_create: block-scaled inputs run with cta_group=1");
     B200_REQUIRE(d.tile_n == 0 || d.tile_n == 128 || d.tile_n == 256, "gemm_plan_create: block-scaled inputs use tile_n=128 or 256 (got %d)", d.tile_n);
   }
   B200_REQUIRE(d.dtype_c == B200_F32 || d.dtype_c == B200_BF16 || d.dtype_c == B200_I32,
@@ -551,7 +568,6 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   // deeper ring; it needs at least one full 256-row tile to pay off and row-major B.
   int cg = d.cta_group != 0 ? d.cta_group : (d.tile_m == 2 * gemm::kBM ? 2 : (d.tile_m == gemm::kBM ? 1 : 0));
   if (cg == 0) cg = (d.b_layout == B200_B_ROW_MAJOR_NK && d.M >= 2 * gemm::kBM && d.tile_n != 32) ? 2 : 1;
-  if (mx) cg = 1;
   plan->cg = cg;
   plan->mx = mx;
   plan->m_blocks = ceil_div(d.M, gemm::kBM * cg);
@@ -561,7 +577,7 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   int bn = d.tile_n;
   if (bn == 0 && mx) {
     // 256 columns unless that leaves SMs without a tile: a 128-column tile is bound by shared-memory reads.
-    bn = (static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, 256) >= kDefaultSms) ? 256 : 128;
+    bn = (static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, 256) >= kDefaultSms / cg) ? 256 : 128;
   }
   if (bn == 0) {
     const int units = kDefaultSms / cg;  // CTAs or pairs that run at once
@@ -684,8 +700,13 @@ int b200_gemm_plan_set_mx_scales(b200_gemm_plan* plan, const void* scales_a_pack
   B200_REQUIRE(scales_a_packed != nullptr && scales_b_packed != nullptr, "gemm_plan_set_mx_scales: NULL scales");
   B200_REQUIRE(((reinterpret_cast<uintptr_t>(scales_a_packed) | reinterpret_cast<uintptr_t>(scales_b_packed)) & 15u) == 0,
                "gemm_plan_set_mx_scales: packed scales must be 16-byte aligned");
-  plan->sfa = static_cast<const uint8_t*>(scales_a_packed);
-  plan->sfb = static_cast<const uint8_t*>(scales_b_packed);
+  const uint64_t k_stages = static_cast<uint64_t>(ceil_div(plan->desc.K, gemm::kRowBytes));
+  int rc = make_scale_map(&plan->map_sfa, scales_a_packed, static_cast<uint64_t>(ceil_div(plan->desc.M, 128)) * k_stages);
+  if (rc != B200_OK) return rc;
+  rc = make_scale_map(&plan->map_sfb, scales_b_packed, static_cast<uint64_t>(ceil_div(plan->desc.N, 128)) * k_stages);
+  if (rc != B200_OK) return rc;
+  plan->sfa = scales_a_packed;
+  plan->sfb = scales_b_packed;
   return B200_OK;
 }
 

@@ -352,46 +352,55 @@ __device__ __forceinline__ void umma_mx_ss(uint32_t tmem_d, uint64_t desc_a, uin
 __device__ __forceinline__ constexpr uint32_t smem_desc_hi_scales() { return (128u >> 4) | (1u << 14); }
 __device__ __forceinline__ uint32_t smem_desc_lo_scales(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
 
-#define B200_MX_MMA(J)                                                                          \
+#define B200_MX_MMA(GROUP, J)                                                                   \
   "add.u32 la, %1, " #J "*2;\n"                                                                 \
   "add.u32 lb, %2, " #J "*2;\n"                                                                 \
   "add.u32 id, %4, " #J "*0x20000010;\n"                                                        \
   "mov.b64 da, {la, %3};\n"                                                                     \
   "mov.b64 db, {lb, %3};\n"                                                                     \
-  "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, id, [%6], [tb], q;\n"
+  "tcgen05.mma.cta_group::" GROUP ".kind::mxf8f6f4.block_scale [%0], da, db, id, [%6], [tb], q;\n"
 
-template <int NB>
+#define B200_MX_STAGE_ASM(GROUP)                                                                \
+  asm volatile(                                                                                 \
+      "{\n"                                                                                     \
+      ".reg .pred p, q;\n"                                                                      \
+      ".reg .b64 da, db, sd;\n"                                                                 \
+      ".reg .b32 la, lb, id, ls, tb, tc;\n"                                                     \
+      "setp.ne.b32 p, %5, 0;\n"                                                                 \
+      "mov.b64 sd, {%7, %8};\n"                                                                 \
+      "tcgen05.cp.cta_group::" GROUP ".32x128b.warpx4 [%6], sd;\n"                              \
+      "add.u32 ls, %7, 32;\n"                                                                   \
+      "add.u32 tb, %6, 4;\n"                                                                    \
+      "mov.b64 sd, {ls, %8};\n"                                                                 \
+      "tcgen05.cp.cta_group::" GROUP ".32x128b.warpx4 [tb], sd;\n"                              \
+      "setp.eq.b32 q, %9, 2;\n"                                                                 \
+      "add.u32 ls, %7, 64;\n"                                                                   \
+      "add.u32 tc, %6, 8;\n"                                                                    \
+      "mov.b64 sd, {ls, %8};\n"                                                                 \
+      "@q tcgen05.cp.cta_group::" GROUP ".32x128b.warpx4 [tc], sd;\n"                           \
+      "setp.eq.b32 q, 0, 0;\n"                                                                  \
+      "mov.b64 da, {%1, %3};\n"                                                                 \
+      "mov.b64 db, {%2, %3};\n"                                                                 \
+      "tcgen05.mma.cta_group::" GROUP ".kind::mxf8f6f4.block_scale [%0], da, db, %4, [%6], [tb], p;\n" \
+      B200_MX_MMA(GROUP, 1) B200_MX_MMA(GROUP, 2) B200_MX_MMA(GROUP, 3) "}\n" ::"r"(tmem_d),     \
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first), "r"(sf_tmem), "r"(sf_lo), "r"(sf_hi), "r"(NB)   \
+      : "memory")
+
+// CTA_GROUP = 2: issued by the leader of a CTA pair; each tcgen05.cp then copies from the same
+// shared-memory offset of both CTAs into each CTA's own TMEM (every CTA holds the scales of its
+// own 128 rows of A and of all columns of the B tile).
+template <int CTA_GROUP, int NB>
 __device__ __forceinline__ void umma_mx_stage(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
                                               uint32_t accumulate_first, uint32_t sf_tmem, uint32_t sf_lo) {
   static_assert(NB == 1 || NB == 2, "one or two 128-row scale blocks of B");
   constexpr uint32_t sf_hi = smem_desc_hi_scales();
-  asm volatile(
-      "{\n"
-      ".reg .pred p, q;\n"
-      ".reg .b64 da, db, sd;\n"
-      ".reg .b32 la, lb, id, ls, tb, tc;\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "setp.eq.b32 q, 0, 0;\n"
-      "mov.b64 sd, {%7, %8};\n"
-      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%6], sd;\n"
-      "add.u32 ls, %7, 32;\n"
-      "add.u32 tb, %6, 4;\n"
-      "mov.b64 sd, {ls, %8};\n"
-      "tcgen05.cp.cta_group::1.32x128b.warpx4 [tb], sd;\n"
-      "setp.eq.b32 q, %9, 2;\n"
-      "add.u32 ls, %7, 64;\n"
-      "add.u32 tc, %6, 8;\n"
-      "mov.b64 sd, {ls, %8};\n"
-      "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [tc], sd;\n"
-      "setp.eq.b32 q, 0, 0;\n"
-      "mov.b64 da, {%1, %3};\n"
-      "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%6], [tb], p;\n"
-      B200_MX_MMA(1) B200_MX_MMA(2) B200_MX_MMA(3)
-      "}\n" ::"r"(tmem_d),
-      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first), "r"(sf_tmem), "r"(sf_lo), "r"(sf_hi), "r"(NB)
-      : "memory");
+  if constexpr (CTA_GROUP == 1) {
+    B200_MX_STAGE_ASM("1");
+  } else {
+    B200_MX_STAGE_ASM("2");
+  }
 }
+#undef B200_MX_STAGE_ASM
 #undef B200_MX_MMA
 
 // Load 32 consecutive fp32 columns of this thread's TMEM lane (warp w may touch lanes

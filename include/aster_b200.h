@@ -248,7 +248,7 @@ int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void
 
 /* ---- block-scaled fp8 (dtype_ab = B200_MXE4M3 | B200_MXE5M2) -----------------------------
  * C = (A * 2^(sa-127)) . (B * 2^(sb-127))^T with sa[M][K/32], sb[N][K/32] bytes.  K % 32 == 0;
- * row-major B; cta_group 1; tile_n 128 or 256.  The kernel streams the scales in blocks of
+ * row-major B; tile_n 128 or 256.  The kernel streams the scales in blocks of
  * [128 rows][4 K blocks]; b200_pack_mx_scales turns row-major scales (device memory,
  * [rows][K/32] bytes) into that order (device memory of b200_mx_scales_bytes bytes, 16-byte
  * aligned).  b200_gemm_plan_set_mx_scales attaches the packed scales of A and B to a plan;

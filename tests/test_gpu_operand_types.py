@@ -170,15 +170,16 @@ class TestBlockScaledFp8:
         want = 32.0 * (np.exp2(sa.astype(np.float64) - 127) @ np.exp2(sb.astype(np.float64) - 127).T)
         assert np.array_equal(got, want.astype(np.float32))  # powers of two: exact
 
+    @pytest.mark.parametrize("cta_group", [1, 2])
     @pytest.mark.parametrize("tile_n", [128, 256])
     @pytest.mark.parametrize("elem", ["e4m3", "e5m2"])
     @pytest.mark.parametrize("shape", [(128, 128, 128), (256, 384, 1024), (200, 136, 160), (1000, 520, 2080), (512, 512, 8192)])
-    def test_against_oracle(self, gpu, elem, shape, tile_n):
+    def test_against_oracle(self, gpu, elem, shape, tile_n, cta_group):
         M, N, K = shape
         a, b, qa, sa, qb, sb = mx_inputs(M, N, K, seed=M + K, elem=elem)
         want = orc.gemm_mx(qa, qb, sa, sb, elem)
         for dtype_c in ("f32", "bf16"):
-            got = gemm(qa, qb, dtype_ab="mx" + elem, dtype_c=dtype_c, block_scales_a=sa, block_scales_b=sb, tile_n=tile_n)
+            got = gemm(qa, qb, dtype_ab="mx" + elem, dtype_c=dtype_c, block_scales_a=sa, block_scales_b=sb, tile_n=tile_n, cta_group=cta_group)
             want_c = orc.decode(orc.encode(want, dtype_c), dtype_c)
             assert orc.rel_frobenius(orc.decode(got, dtype_c), want_c) <= 1e-3
         # against the unquantised product the error is the quantisation noise of the format
@@ -192,14 +193,13 @@ class TestBlockScaledFp8:
         want = np.maximum(orc.gemm_mx(qa, qb, sa, sb) + bias[None, :], 0)
         kw = dict(dtype_ab="mxe4m3", dtype_c="f32", block_scales_a=sa, block_scales_b=sb, bias=bias, relu=True)
         for extra in ({}, {"split_k": 3}, {"max_ctas": 4, "tail_split": True}, {"stages": 2}, {"tile_n": 256}, {"tile_n": 256, "max_ctas": 2},
-                      {"tile_n": 256, "split_k": 2, "stages": 3}):
+                      {"tile_n": 256, "split_k": 2, "stages": 3}, {"cta_group": 1}, {"cta_group": 1, "tile_n": 128, "max_ctas": 3, "tail_split": True},
+                      {"cta_group": 2, "tile_n": 128, "split_k": 2}, {"cta_group": 2, "tile_n": 256, "max_ctas": 2, "tail_split": True}):
             assert orc.rel_frobenius(gemm(qa, qb, **kw, **extra), want) <= 1e-3, extra
 
     def test_refusals(self, gpu):
         with pytest.raises(nat.B200Error, match="K %% 32 == 0|K % 32 == 0"):
             GemmPlan(128, 128, 144, "mxe4m3", "f32")
-        with pytest.raises(nat.B200Error, match="cta_group=1"):
-            GemmPlan(256, 128, 128, "mxe4m3", "f32", cta_group=2)
         with pytest.raises(nat.B200Error, match="tile_n=128 or 256"):
             GemmPlan(256, 256, 128, "mxe4m3", "f32", tile_n=64)
         with pytest.raises(nat.B200Error, match="not block-scaled"):
