@@ -94,7 +94,8 @@ struct Params {
   uint32_t* tail_flags;   // [tail_tiles][tail_parts - 1][CG][4 epilogue warps]
   uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
   int debug_mode;  // bits 0-1: 1 = producer signals without copying, 2 = MMA warp commits without multiplying;
-                   // bit 2: skip the tail-split exchange; bit 3: producer never signals (exercises the wait limit)
+                   // bit 2: skip the tail-split exchange; bit 3: producer never signals (exercises the wait limit);
+                   // bit 4 (host only): launch without programmatic stream serialisation
   unsigned wait_limit_ms;  // limit of every bounded wait; 0 = default
 };
 
@@ -427,6 +428,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Everything above touched only this CTA's shared and tensor memory.  From here on global
+  // memory is read and written, so the previous kernel of the stream must be complete; the next
+  // one may already set itself up behind this one (it waits at this same point).
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     // ------------------------------- producer -------------------------------

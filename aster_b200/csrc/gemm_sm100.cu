@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -466,22 +467,33 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     p.epoch = ++plan->epoch;
     if (p.epoch == 0) p.epoch = ++plan->epoch;  // 0 is the cleared state of a flag
   }
-  if (plan->cg == 2) {
+  {
+    // Programmatic stream serialisation: this launch may begin its prologue (barrier set-up,
+    // TMEM allocation, descriptor prefetch) while the previous kernel of the stream drains; the
+    // kernel waits for that kernel's completion before it touches global memory.
+    static const bool pdl_off = std::getenv("ASTER_B200_NO_PDL") != nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(plan->grid));
     cfg.blockDim = dim3(gemm::kThreads);
     cfg.dynamicSmemBytes = static_cast<size_t>(plan->smem);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (plan->cg == 2) {
+      attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+      attr[n_attr].val.clusterDim.x = 2;
+      attr[n_attr].val.clusterDim.y = 1;
+      attr[n_attr].val.clusterDim.z = 1;
+      ++n_attr;
+    }
+    if (!pdl_off && (d.reserved[0] & 16) == 0) {
+      attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+      ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = n_attr;
     B200_CUDA_OK(cudaLaunchKernelEx(&cfg, plan->kernel, plan->map_a, plan->map_b, plan->map_sfa, plan->map_sfb, p));
-  } else {
-    plan->kernel<<<plan->grid, gemm::kThreads, plan->smem, stream>>>(plan->map_a, plan->map_b, plan->map_sfa, plan->map_sfb, p);
   }
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());

@@ -306,6 +306,13 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_format, uint32_t a_
   return (d_format << 4) | (a_format << 7) | (b_format << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
 }
 
+// Programmatic dependent launch.  `griddep_launch_dependents` lets the next kernel of the stream
+// (if it was launched with programmatic stream serialisation) start its own prologue while this
+// grid is still running; `griddep_wait` blocks until every grid this one depends on has finished
+// and its memory is visible.  Both do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- block-scaled 8-bit floats (kind::mxf8f6f4): one E8M0 scale per 32 elements of K ----
 // Instruction descriptor of the block-scaled kinds (accumulators are always f32):
 //   bits 4-5 scale id of B   bits 7-9 A format   bits 10-12 B format   bits 17-22 N >> 3
