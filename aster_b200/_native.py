@@ -156,6 +156,7 @@ SIGNATURES = {
     "b200_vector_add_f32": [_P, _P, _P, _SZ, _P],
     "b200_copy_2d_padded_f32": [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, _P],
     "b200_add_relu_f32": [_P, _P, _P, _SZ, _P],
+    "b200_gemm_debug_timeline": [_P, _P],
     "b200_mx_scales_bytes": [C.c_int64, C.c_int64, C.POINTER(_SZ)],
     "b200_pack_mx_scales": [_P, _P, C.c_int64, C.c_int64, _P],
     "b200_gemm_plan_set_mx_scales": [_P, _P, _P],

@@ -95,9 +95,22 @@ struct Params {
   uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
   int debug_mode;  // bits 0-1: 1 = producer signals without copying, 2 = MMA warp commits without multiplying;
                    // bit 2: skip the tail-split exchange; bit 3: producer never signals (exercises the wait limit);
-                   // bit 4 (host only): launch without programmatic stream serialisation
+                   // bit 4 (host only): launch without programmatic stream serialisation; bit 5: the epilogue
+                   // computes but does not store C (isolates the cost of the stores); bit 6: 16-byte stores only
   unsigned wait_limit_ms;  // limit of every bounded wait; 0 = default
+  // Non-zero: nothing that precedes a launch in its stream writes B (a weight matrix), so the
+  // producer may request the first ring of B tiles before the previous kernel has completed.
+  int static_b;
+  // Bring-up aid: when non-null, every CTA writes global-timer readings (ns) of its milestones to
+  // timeline[blockIdx.x * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel complete,
+  // 3 first copy issued, 4 first stage landed, 5 last MMA committed, 6 last accumulator ready,
+  // 7 last epilogue done, 8 exit, 9..15 last MMA of the CTA's first seven work items committed.
+  unsigned long long* timeline;
 };
+
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+  if (p.timeline != nullptr) p.timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = sm100::globaltimer_ns();
+}
 
 // Block-scaled (MX) stages carry the E8M0 scales of their 128 elements of K behind the operand
 // tiles: one 512-byte block for the 128 rows of A and one per 128 rows of B, padded so that
@@ -308,25 +321,37 @@ struct OutVec<__nv_bfloat16> {
 };
 
 // Store 32 consecutive outputs of one row.  `vec_ok`: the row segment is 16-byte aligned and
-// entirely inside the matrix.
+// entirely inside the matrix; `wide_ok`: it is 32-byte aligned as well.
 template <typename OutT>
-__device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], bool vec_ok, int valid) {
+__device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], bool vec_ok, int valid, bool wide_ok = false) {
   if (vec_ok) {
     if constexpr (sizeof(OutT) == 4) {
-      float4* d4 = reinterpret_cast<float4*>(dst);
+      if (wide_ok) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) d4[j] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
-    } else {
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(x[8 * j + 2 * t], x[8 * j + 2 * t + 1]);
-          w[t] = *reinterpret_cast<uint32_t*>(&h);
+        for (int j = 0; j < 4; ++j) {
+          sm100::st_global_v8(dst + 8 * j, __float_as_uint(x[8 * j]), __float_as_uint(x[8 * j + 1]), __float_as_uint(x[8 * j + 2]),
+                              __float_as_uint(x[8 * j + 3]), __float_as_uint(x[8 * j + 4]), __float_as_uint(x[8 * j + 5]),
+                              __float_as_uint(x[8 * j + 6]), __float_as_uint(x[8 * j + 7]));
         }
-        d4[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      } else {
+        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d4[j] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+      }
+    } else {
+      uint32_t w[16];
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * t], x[2 * t + 1]);
+        w[t] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      if (wide_ok) {
+        sm100::st_global_v8(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+        sm100::st_global_v8(dst + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+      } else {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d4[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
       }
     }
   } else {
@@ -395,6 +420,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     t_cycles = clock64();
     t_ns = globaltimer_ns();
   }
+  if (threadIdx.x == 0) stamp(p, 0);
   const Waiter waiter{abort_flag, p.status, p.wait_limit_ms != 0 ? p.wait_limit_ms * 1000000ull : kWaitTimeoutNs};
   const int num_items = num_work_items(p);
   const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;  // position in the pair
@@ -431,12 +457,59 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // Everything above touched only this CTA's shared and tensor memory.  From here on global
   // memory is read and written, so the previous kernel of the stream must be complete; the next
   // one may already set itself up behind this one (it waits at this same point).
+  if (threadIdx.x == 0) stamp(p, 1);
   griddep_launch_dependents();
-  griddep_wait();
+  if (warp != 0 || p.static_b == 0) griddep_wait();  // the producer of a static-B plan waits after its early B requests
+  if (threadIdx.x == 32) stamp(p, 2);
 
   if (warp == 0) {
     // ------------------------------- producer -------------------------------
     // The whole warp walks the loop (every lane polls the barrier); one elected lane issues.
+    // B tile of ring slot `stg` for K block `kb_abs` (called by the elected lane).
+    auto issue_b = [&](int stg, int n_blk_, int b_row_, int kb_abs) {
+      const uint32_t b_dst = smem_base + stg * kStageBytes + kABytes;
+      const int k_elem = kb_abs * p.kb_elems;
+      if constexpr (CG == 1) {
+        if (p.b_packed != nullptr) {
+          const size_t blk = static_cast<size_t>(n_blk_) * (static_cast<size_t>(p.num_kb) * p.split_k) + kb_abs;
+          bulk_load_1d(b_dst, static_cast<const uint8_t*>(p.b_packed) + blk * kBBytes, kBBytes, full_bar(stg));
+        } else {
+          tma_load_2d(b_dst, &tmap_b, full_bar(stg), k_elem, b_row_);
+        }
+      } else {
+        tma_load_2d_pair(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_);
+      }
+    };
+    // Arm the slot's barrier with the bytes of all copies of the stage (both CTAs' in a pair,
+    // where every copy completes on the leader's barrier).
+    auto arm = [&](int stg) {
+      if constexpr (CG == 1) {
+        mbar_arrive_expect_tx(full_bar(stg), kLoadBytes);
+      } else {
+        if (leader) mbar_arrive_expect_tx(full_bar(stg), 2u * kLoadBytes);
+      }
+    };
+    // Static B: the first ring of B tiles is requested before the previous kernel of the stream
+    // has completed; everything else (A, scales, all writes) comes after griddep_wait.
+    int pre = 0;
+    if (p.static_b != 0) {
+      if ((p.debug_mode & 11) == 0 && first_item < num_items) {
+        const WorkItem w = decode_item(p, first_item);
+        int m_blk, n_blk;
+        tile_coords(p, w.tile, m_blk, n_blk);
+        const int b_row = n_blk * BN + static_cast<int>(cta_rank * kBRows);
+        pre = min(p.stages, w.nkb);
+        if (elect_one()) {
+          stamp(p, 3);
+          for (int kb = 0; kb < pre; ++kb) {
+            arm(kb);
+            issue_b(kb, n_blk, b_row, w.kb0 + kb);
+          }
+        }
+        __syncwarp();
+      }
+      griddep_wait();
+    }
     int stage = 0;
     uint32_t phase = 0;
     long long issued = 0;
@@ -454,7 +527,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           ok = false;
           break;
         }
+        const bool b_requested = item == first_item && kb < pre;  // armed and B on its way since before the wait
         if (elect_one()) {
+          if (issued == 0 && pre == 0) stamp(p, 3);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const int k_elem = (kb0 + kb) * p.kb_elems;
@@ -470,7 +545,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else if ((p.debug_mode & 3) == 1) {
             if (leader) mbar_arrive(full_bar(stage));
           } else if constexpr (CG == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), kLoadBytes);
+            if (!b_requested) arm(stage);
             if constexpr (MX) {
               tma_load_2d(sf_dst, &tmap_sfa, full_bar(stage), 0, sfa_blk * p.sf_k_stages + ks);
 #pragma unroll
@@ -479,17 +554,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               }
             }
             tma_load_2d(a_dst, &tmap_a, full_bar(stage), k_elem, a_row);
-            if (p.b_packed != nullptr) {
-              const size_t blk = static_cast<size_t>(n_blk) * (static_cast<size_t>(p.num_kb) * p.split_k) + (kb0 + kb);
-              bulk_load_1d(b_dst, static_cast<const uint8_t*>(p.b_packed) + blk * kBBytes, kBBytes, full_bar(stage));
-            } else {
-              tma_load_2d(b_dst, &tmap_b, full_bar(stage), k_elem, b_row);
-            }
+            if (!b_requested) issue_b(stage, n_blk, b_row, kb0 + kb);
           } else {
             // Both CTAs' copies complete on the leader's barrier, which the leader arms with
             // the byte count of the pair.
             const uint32_t leader_full = map_to_cta(full_bar(stage), 0u);
-            if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * kLoadBytes);
+            if (!b_requested) arm(stage);
             if constexpr (MX) {
               tma_load_2d_pair(sf_dst, &tmap_sfa, leader_full, 0, sfa_blk * p.sf_k_stages + ks);
 #pragma unroll
@@ -498,7 +568,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               }
             }
             tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, a_row);
-            tma_load_2d_pair(b_dst, &tmap_b, leader_full, k_elem, b_row);
+            if (!b_requested) issue_b(stage, n_blk, b_row, kb0 + kb);
           }
         }
         __syncwarp();
@@ -540,6 +610,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t idesc = p.idesc;
       [[maybe_unused]] uint32_t sf_set = 0;
       const int stages = p.stages;
+      bool first_stage = true;
       for (int item = first_item; ok && item < num_items; item += item_stride) {
         const WorkItem w = decode_item(p, item);
         const int tile = w.tile;
@@ -556,6 +627,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             break;
           }
           tc_fence_after_sync();
+          if (first_stage) {
+            first_stage = false;
+            if (lane == 0) stamp(p, 4);
+          }
           if (elect_one()) {
             if constexpr (MX) {
               // Scales of this stage: shared memory -> TMEM (alternating column sets), then the
@@ -589,6 +664,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if constexpr (CG == 2) umma_commit<CG>(acc_full_bar(acc) + peer_delta);
         }
         __syncwarp();
+        if (lane == 0) {
+          stamp(p, 5);  // overwritten per item: the last one stays
+          const int nth = (item - first_item) / item_stride;
+          if (nth < 7) stamp(p, 9 + nth);  // commit time of this CTA's first seven work items
+        }
         acc = (acc + 1) % kAccBufs;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -602,12 +682,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else {
     // ------------------------------- epilogue -------------------------------
     const int quarter = warp & 3;  // TMEM lanes this warp may read
+    // One warp per lane quarter.  (Two warps per quarter, each taking half of the columns, made
+    // every launch slower: the tail of a launch is bound by the rate of store requests, not by
+    // the number of epilogue chains, and the extra warps cost registers and power.)
+    constexpr int c_begin = 0;
+    constexpr int c_end = BN;
     const int row_in_tile = static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
     float alpha = 1.0f;
     if (p.scale_a != nullptr) alpha *= __ldg(p.scale_a);
     if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
     OutT* const C = static_cast<OutT*>(p.C);
     const bool n_vec_ok = (p.N % OutVec<OutT>::kPerVec) == 0;
+    // 32-byte stores: every row segment starts on a 32-byte boundary (chunks start at multiples of 32 columns)
+    const bool n_wide_ok = (p.N % (2 * OutVec<OutT>::kPerVec)) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 31u) == 0 && (p.debug_mode & 64) == 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -622,6 +709,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         break;
       }
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) stamp(p, 6);  // overwritten per item: the last one stays
       const int row = m_blk * kTileM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -632,8 +720,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // owner use the same lane <-> (row, column) mapping.  Every exchange access is therefore a
       // fully coalesced 512-byte warp access; a row-major exchange was 8x slower end to end.
       const size_t tail_tile_elems = static_cast<size_t>(kTileM) * BN;
-      const int flag_lane = (static_cast<int>(cta_rank) * 4 + quarter);
-      const size_t warp_slab = static_cast<size_t>(flag_lane) * (32u * BN);  // floats per warp = 32 rows x BN
+      const int flag_lane = static_cast<int>(cta_rank) * 4 + quarter;  // one flag per epilogue warp
+      const size_t warp_slab = static_cast<size_t>(static_cast<int>(cta_rank) * 4 + quarter) * (32u * BN);  // floats per lane quarter = 32 rows x BN
       // A warp whose 32 rows all lie beyond M has nothing to read, exchange or store.
       const bool slab_ok = (m_blk * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32) < p.M;
       const bool exchange = (p.debug_mode & 4) == 0 && slab_ok;
@@ -648,27 +736,36 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (!ok) break;
       }
-      // Owner: this lane's float4 column of the first contributor's partial tile, chunk 0 loaded now.
+      // Owner: this lane's float4 column of the first contributor's partial tile, first chunk loaded now.
       const float4* tail_src = reinterpret_cast<const float4*>(
                                    p.tail_ws + static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) * tail_tile_elems + warp_slab) + lane;
       float4 ahead[8];
       if (w.part == 0 && exchange) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + j * 32);
+        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + static_cast<size_t>(c_begin) * 8u + j * 32);
       }
+      // One 32-column chunk of this warp's rows per iteration.  (Keeping the next chunk's TMEM
+      // load in flight during the current one costs 32 more live registers, which the compiler
+      // could only find by spilling -- not an option for registers that an asynchronous load is
+      // still writing.)
 #pragma unroll 1
-      for (int c = 0; c < (slab_ok ? BN : 0); c += 32) {
+      for (int c = c_begin; c < (slab_ok ? c_end : c_begin); c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(c), v);
         tmem_ld_wait();
+        float x[32];
+        if (p.acc_int == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = static_cast<float>(static_cast<int>(v[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+        }
         const int col0 = n_blk * BN + c;
         if (col0 >= p.N) continue;  // warp-uniform
         const int valid = min(32, p.N - col0);
-        float x[32];
         if (p.split_k > 1) {
           // Partial sums go to the workspace untouched; the reduction applies the epilogue.
-#pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
           if (row_ok) {
             float* wdst = p.workspace + (static_cast<size_t>(split) * p.M + row) * p.N + col0;
             store_row32<float>(wdst, x, (p.N % 4) == 0 && valid == 32, valid);
@@ -677,8 +774,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (w.part > 0) {
           // Contributor: hand the raw fp32 tile to the owner (whole rows, ragged edges included).
-#pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
           float4* wdst = reinterpret_cast<float4*>(p.tail_ws + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (w.part - 1)) * tail_tile_elems +
                                                    warp_slab + static_cast<size_t>(c) * 32u) + lane;
           if (exchange) {
@@ -687,20 +782,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           continue;
         }
-        if (p.acc_int != 0) {
-          // Integer accumulators never take part in a K split (the plan refuses it).
-          if (p.acc_int == 2) {
-            // The 32-bit words are moved, not converted: C receives the s32 sums bit for bit.
-#pragma unroll
-            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
-            if (row_ok) store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid);
-            continue;
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = static_cast<float>(static_cast<int>(v[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+        if (p.acc_int == 2) {
+          // Integer sums (never part of a K split: the plan refuses it) are moved, not converted:
+          // C receives the s32 words bit for bit.
+          if (row_ok) store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid);
+          continue;
         }
         if (w.part == 0 && exchange) {
           // The first contributor's chunk was fetched one iteration ahead (`ahead`); further
@@ -712,7 +798,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             x[4 * j + 2] += ahead[j].z;
             x[4 * j + 3] += ahead[j].w;
           }
-          if (c + 32 < BN) {
+          if (c + 32 < c_end) {
             const float4* nxt = tail_src + static_cast<size_t>(c + 32) * 8u;
 #pragma unroll
             for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(nxt + j * 32);
@@ -744,7 +830,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
         }
-        if (row_ok) store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid);
+        if (row_ok && (p.debug_mode & 32) == 0) {
+          store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
+        }
       }
       if (w.part > 0 && exchange) {
         // Publish: every lane's stores are ordered before the flag the owner polls.
@@ -766,6 +854,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       acc = (acc + 1) % kAccBufs;
       if (acc == 0) acc_phase ^= 1u;
+      if (warp == 2 && lane == 0) stamp(p, 7);  // overwritten per item: the last one stays
     }
   }
 
@@ -777,6 +866,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) stamp(p, 8);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     const unsigned long long cyc = static_cast<unsigned long long>(clock64() - t_cycles);
     const unsigned long long ns = globaltimer_ns() - t_ns;

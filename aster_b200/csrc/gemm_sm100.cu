@@ -241,6 +241,7 @@ struct b200_gemm_plan {
   const void* sfa = nullptr;
   const void* sfb = nullptr;
   CUtensorMap map_sfa = {}, map_sfb = {};  // all zero (never dereferenced) unless mx
+  unsigned long long* timeline = nullptr;  // bring-up aid, see b200_gemm_debug_timeline
   int stages = 0;
   int split_k = 1;
   int grid = 0;
@@ -285,7 +286,7 @@ int64_t packed_b_bytes(const b200_gemm_plan* p) {
 void plan_tail_split(b200_gemm_plan* plan) {
   plan->tail_tiles = plan->tail_parts = plan->tail_kb0 = plan->tail_kb = 0;
   plan->tail_ws_bytes = plan->tail_flag_bytes = 0;
-  if (plan->split_k > 1 || plan->desc.reserved[1] == 1) return;  // reserved[1] = 1: caller opted out
+  if (plan->split_k > 1 || (plan->desc.reserved[1] & 1) != 0) return;  // reserved[1] bit 0: caller opted out
   if (plan->desc.dtype_ab == B200_I8) return;  // partial tiles are exchanged as fp32; s32 sums stay whole
   const int units = plan->units_cap;
   const int tiles = plan->m_blocks * plan->n_blocks;
@@ -299,7 +300,7 @@ void plan_tail_split(b200_gemm_plan* plan) {
   if (parts < 2) return;
   // The owner (part 0) takes a few more K blocks than the contributors, so that their partial
   // tiles are already in the workspace when the owner's own MMAs finish.
-  int kb0 = (plan->num_kb + parts - 1) / parts + 5;
+  int kb0 = (plan->num_kb + parts - 1) / parts + 5;  // measured: 0..3 and 8 are slower on the large and the skinny shapes
   if (kb0 > plan->num_kb - (parts - 1)) kb0 = plan->num_kb - (parts - 1);
   const int rest = plan->num_kb - kb0;
   const int tail_kb = (rest + parts - 2) / (parts - 1);
@@ -309,7 +310,7 @@ void plan_tail_split(b200_gemm_plan* plan) {
   plan->tail_parts = parts;
   plan->tail_kb0 = kb0;
   plan->tail_kb = tail_kb;
-  const int64_t flags = static_cast<int64_t>(tail) * (parts - 1) * plan->cg * 4 * sizeof(uint32_t);
+  const int64_t flags = static_cast<int64_t>(tail) * (parts - 1) * plan->cg * gemm::kEpilogueWarps * sizeof(uint32_t);
   plan->tail_flag_bytes = (flags + 255) / 256 * 256;
   plan->tail_ws_bytes = plan->tail_flag_bytes +
                         static_cast<int64_t>(tail) * (parts - 1) * (gemm::kBM * plan->cg) * plan->bn * sizeof(float);
@@ -448,6 +449,8 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.b_packed = direct_b(plan) ? B : nullptr;
   p.workspace = static_cast<float*>(workspace);
   p.status = plan->status;
+  p.timeline = plan->timeline;
+  p.static_b = (d.reserved[1] & 2) != 0 ? 1 : 0;
   p.debug_mode = d.reserved[0];
   p.wait_limit_ms = d.reserved[2] > 0 ? static_cast<unsigned>(d.reserved[2]) : 0u;
   if (plan->tail_parts > 1 && workspace != nullptr && static_cast<int64_t>(workspace_size) >= plan->tail_ws_bytes &&
@@ -682,6 +685,13 @@ int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, vo
       plan->n_blocks, plan->total_kb, plan->desc.b_layout == B200_B_REF_PRESHUFFLED ? 1 : 0);
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_gemm_debug_timeline(b200_gemm_plan* plan, void* device_buffer) {
+  B200_REQUIRE(plan != nullptr, "gemm_debug_timeline: plan is NULL");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(device_buffer) & 7u) == 0, "gemm_debug_timeline: buffer must be 8-byte aligned");
+  plan->timeline = static_cast<unsigned long long*>(device_buffer);
   return B200_OK;
 }
 

@@ -306,6 +306,15 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_format, uint32_t a_
   return (d_format << 4) | (a_format << 7) | (b_format << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
 }
 
+// 32-byte global store (sm_100): half as many store requests as two 16-byte stores, which is
+// what bounds an epilogue whose lanes each write their own row.
+__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
+                                             uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+
 // Programmatic dependent launch.  `griddep_launch_dependents` lets the next kernel of the stream
 // (if it was launched with programmatic stream serialisation) start its own prologue while this
 // grid is still running; `griddep_wait` blocks until every grid this one depends on has finished

@@ -39,7 +39,9 @@ class GemmPlan:
     """A validated problem description bound to a kernel instance.
 
     Parameters mirror ``b200_gemm_desc``.  ``tile_n``, ``stages``, ``split_k`` = 0 let the
-    library choose (``split_k=-1``: choose a K split for skinny problems).
+    library choose (``split_k=-1``: choose a K split for skinny problems).  ``static_b=True``
+    declares that nothing enqueued before a launch in its stream writes B (a weight matrix):
+    the kernel may then request its first B tiles while the previous kernel is still finishing.
     """
 
     def __init__(
@@ -65,6 +67,7 @@ class GemmPlan:
         debug_mode: int = 0,
         no_tail_split: bool = False,
         wait_limit_ms: int = 0,
+        static_b: bool = False,
     ) -> None:
         self._handle = None
         desc = nat.GemmDesc()
@@ -81,7 +84,7 @@ class GemmPlan:
         desc.stages, desc.cta_group, desc.split_k = stages, cta_group, split_k
         desc.max_ctas, desc.raster_group = max_ctas, raster_group
         desc.reserved[0] = debug_mode  # kernel bring-up aid: 1 = no copies, 2 = no multiplies (results are garbage)
-        desc.reserved[1] = 1 if no_tail_split else 0
+        desc.reserved[1] = (1 if no_tail_split else 0) | (2 if static_b else 0)
         desc.reserved[2] = wait_limit_ms
         desc.label = label.encode()[:255]
         handle = C.c_void_p()

@@ -56,10 +56,11 @@ WORKLOADS = {
                             "on the device), N(0,1) seed 8, bf16 out"),
     "sharded_65536": dict(M=65536, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, strong=True,
                           text="bf16 GEMM M=65536 N=K=8192 split by M rows over the GPUs, U(-1,1) seed 4"),
-    "decode_16": dict(M=16, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True,
-                      text="bf16 skinny GEMM M=16 N=K=8192, U(-1,1) seed 4"),
-    "decode_128": dict(M=128, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True,
-                       text="bf16 skinny GEMM M=128 N=K=8192, U(-1,1) seed 4"),
+    "decode_16": dict(M=16, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True, static_b=True,
+                      text="bf16 skinny GEMM M=16 N=K=8192, U(-1,1) seed 4; B is the weight matrix (static_b: its first tiles are "
+                           "requested while the previous launch drains)"),
+    "decode_128": dict(M=128, N=8192, K=8192, dtype_ab="bf16", dtype_c="bf16", dist="uniform", seed=4, tile_n=128, hbm=True, static_b=True,
+                       text="bf16 skinny GEMM M=128 N=K=8192, U(-1,1) seed 4; B is the weight matrix (static_b)"),
     "vector_add": dict(n=1 << 28, text="int32 vector_add, 2^28 elements per array, integers from default_rng(5)"),
     "vector_add_64m": dict(n=1 << 26, text="int32 vector_add, 2^26 elements per array (profiling size), integers from default_rng(5)"),
     "copy_2d_padded_8k": dict(M=8192, N=8188, text="fp32 copy_2d_padded 8192x8188 (profiling size), standard normal from default_rng(6)"),
@@ -414,7 +415,7 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
     world = job.world
     rows = w["M"] // world if w.get("strong") else w["M"]
     N, K = w["N"], w["K"]
-    plan_kw = {k: w[k] for k in ("epilogue", "split_k", "tile_n") if k in w}
+    plan_kw = {k: w[k] for k in ("epilogue", "split_k", "tile_n", "static_b") if k in w}
     plan = GemmPlan(rows, N, K, w["dtype_ab"], w["dtype_c"], **plan_kw)
     res = plan.resources()
     ops = host_operands(w, job.rank, rows)

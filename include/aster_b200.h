@@ -141,8 +141,12 @@ typedef struct b200_gemm_desc {
   int32_t max_ctas;  /* persistent grid size cap; 0 = number of SMs                             */
   int32_t raster_group; /* m-blocks per rasterisation group; 0 = choose                         */
   int32_t reserved[3];  /* [0] kernel bring-up mode (0 = normal; 8 = the producer never hands a stage
-                         * over, which makes the consumer's bounded wait expire), [1] 1 = never use
-                         * the tail split, [2] limit of the device-side waits in ms (0 = 2000) */
+                         * over, which makes the consumer's bounded wait expire; 16 = launch without
+                         * programmatic stream serialisation), [1] bit 0 = never use the tail split,
+                         * bit 1 = B is static: nothing enqueued before a launch in its stream writes
+                         * B (a weight matrix), so the kernel may request its first B tiles while the
+                         * previous kernel of the stream is still finishing, [2] limit of the
+                         * device-side waits in ms (0 = 2000) */
   char label[256];   /* provenance only: the reference label string (gemm_config.py:678-701)    */
 } b200_gemm_desc;
 
@@ -245,6 +249,14 @@ int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, 
                             int num_ctas, void* stream);
 /* out[i] = max(a[i] + b[i], 0); examples/07_simple_fusion/simple_fusion.py:62-144. */
 int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void* stream);
+
+/* Bring-up aid (no counterpart in the reference): with a device buffer of grid_ctas * 16
+ * uint64 words attached, every CTA of the plan's launches records global-timer readings (ns)
+ * of its milestones at [cta * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel of the
+ * stream complete, 3 first copy issued, 4 first stage landed, 5 last MMA committed, 6 last
+ * accumulator ready, 7 last epilogue done, 8 exit, 9..15 the MMAs of the CTA's first seven work
+ * items committed.  NULL detaches. */
+int b200_gemm_debug_timeline(b200_gemm_plan* plan, void* device_buffer);
 
 /* ---- block-scaled fp8 (dtype_ab = B200_MXE4M3 | B200_MXE5M2) -----------------------------
  * C = (A * 2^(sa-127)) . (B * 2^(sb-127))^T with sa[M][K/32], sb[N][K/32] bytes.  K % 32 == 0;

@@ -452,3 +452,50 @@ class TestPlanObject:
         assert plan.resources().regs_per_thread > 0
         for b in bufs:
             b.free()
+
+
+class TestDependentLaunch:
+    """Launches use programmatic stream serialisation: a kernel may set itself up, and with
+    ``static_b`` request its first B tiles, while the previous kernel of the stream finishes.
+    Whatever one launch reads from the previous one must still be complete."""
+
+    def test_second_gemm_reads_the_first_ones_output(self, gpu):
+        from aster_b200 import _native as nat
+        from aster_b200.execution import GpuBuffer
+
+        M, K1, N1, N2 = 256, 4096, 2048, 512  # C1 [M, N1] is the A operand of the second product
+        rng = np.random.default_rng(3)
+        a1 = orc.encode(rng.uniform(-1, 1, (M, K1)).astype(np.float32), "bf16")
+        b1 = orc.encode(rng.uniform(-1, 1, (N1, K1)).astype(np.float32) / 64, "bf16")
+        b2 = orc.encode(rng.uniform(-1, 1, (N2, N1)).astype(np.float32), "bf16")
+        p1 = GemmPlan(M, N1, K1, "bf16", "bf16")
+        p2 = GemmPlan(M, N2, N1, "bf16", "f32", static_b=True)
+        bufs = [GpuBuffer(x.nbytes) for x in (a1, b1, b2)]
+        for buf, x in zip(bufs, (a1, b1, b2)):
+            buf.copy_from_host(x)
+        c1, c2 = GpuBuffer(M * N1 * 2), GpuBuffer(M * N2 * 4)
+        results = []
+        for _ in range(3):  # back to back, no synchronisation between the two launches
+            c1.zero()
+            c2.zero()
+            p1.run(bufs[0], bufs[1], c1)
+            p2.run(c1, bufs[2], c2)
+            nat.call("b200_device_synchronize")
+            h1, h2 = np.empty((M, N1), np.uint16), np.empty((M, N2), np.float32)
+            c1.copy_to_host(h1)
+            c2.copy_to_host(h2)
+            results.append((h1, h2))
+        h1, h2 = results[0]
+        check(h1, dict(A=a1, B=b1, scale_a=None, scale_b=None), "bf16", "bf16")
+        check(h2, dict(A=h1, B=b2, scale_a=None, scale_b=None), "bf16", "f32")  # from the bits the first launch wrote
+        assert all(np.array_equal(h1, r[0]) and np.array_equal(h2, r[1]) for r in results[1:])
+
+    @pytest.mark.parametrize("shape,kw", [((16, 1024, 4096), dict(tile_n=128, tail_split=True)), ((512, 512, 1024), {}),
+                                           ((300, 200, 520), dict(cta_group=1, b_layout="packed"))])
+    def test_static_b_does_not_change_results(self, gpu, shape, kw):
+        inp = orc.make_inputs(*shape, "bf16", "uniform", 6)
+        plain = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", **kw)
+        early = [gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", static_b=True, **kw) for _ in range(2)]
+        assert np.array_equal(plain, early[0]) and np.array_equal(plain, early[1])
+        no_pdl = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", debug_mode=16, **kw)
+        assert np.array_equal(plain, no_pdl)
