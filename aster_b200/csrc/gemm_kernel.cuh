@@ -83,15 +83,16 @@ struct Params {
   float* workspace;      // split-K partial sums [split][M][N] fp32
   uint32_t* status;
   // Tail split: when the last round of tiles would leave most units idle, each of the
-  // `tail_tiles` last tiles is cut into `tail_parts` K ranges handled by different units; part 0
-  // owns the tile and adds the other parts' fp32 partial tiles (exchanged through `tail_ws`,
-  // announced through `tail_flags` = epoch) before its epilogue.  tail_parts <= 1: off.
+  // `tail_tiles` last tiles is cut into `tail_parts` K ranges handled by different units; each
+  // part then finishes 1/tail_parts of the tile's columns, adding the other parts' fp32 partial
+  // sums for that slice (exchanged through `tail_ws`, announced through `tail_flags` = epoch).
+  // tail_parts <= 1: off.
   int tail_tiles;
   int tail_parts;
-  int tail_kb0;           // K blocks of part 0 (the owner: a few more, so that the others finish first)
+  int tail_kb0;           // K blocks of part 0 (equal to tail_kb)
   int tail_kb;            // K blocks of every other part
-  float* tail_ws;         // [tail_tiles][tail_parts - 1][tile rows][BN] fp32
-  uint32_t* tail_flags;   // [tail_tiles][tail_parts - 1][CG][4 epilogue warps]
+  float* tail_ws;         // [tail_tiles][tail_parts][tile rows][BN] fp32, a part writes only the other parts' slices
+  uint32_t* tail_flags;   // [tail_tiles][tail_parts][CG][4 epilogue warps]
   uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
   int debug_mode;  // bits 0-1: 1 = producer signals without copying, 2 = MMA warp commits without multiplying;
                    // bit 2: skip the tail-split exchange; bit 3: producer never signals (exercises the wait limit);
@@ -725,31 +726,63 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // A warp whose 32 rows all lie beyond M has nothing to read, exchange or store.
       const bool slab_ok = (m_blk * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32) < p.M;
       const bool exchange = (p.debug_mode & 4) == 0 && slab_ok;
-      if (w.part == 0 && exchange) {
-        // Owner: the contributors' partial sums for these 32 rows must have landed.
-        for (int q = 1; q < p.tail_parts; ++q) {
-          const uint32_t* flag = p.tail_flags + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (q - 1)) * (CG * 4) + flag_lane;
-          if (!wait_flag(flag, p.epoch, waiter, tile)) {
-            ok = false;
-            break;
-          }
-        }
-        if (!ok) break;
-      }
-      // Owner: this lane's float4 column of the first contributor's partial tile, first chunk loaded now.
-      const float4* tail_src = reinterpret_cast<const float4*>(
-                                   p.tail_ws + static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) * tail_tile_elems + warp_slab) + lane;
-      float4 ahead[8];
-      if (w.part == 0 && exchange) {
+      // Tail split: the parts of a tile (equal K ranges on different units) each finish one
+      // slice of its columns.  A part first exports its partial sums for the *other* parts'
+      // slices, raises its flag, waits for the others' flags and then adds their partial sums
+      // to its own slice -- a reduce-scatter among the parts.  Every unit exchanges and
+      // finishes 1/parts of the tile, where a single owner used to read and finish all of it.
+      const bool tail_item = w.part >= 0;
+      int lo = c_begin, hi = slab_ok ? c_end : c_begin;  // the columns this warp finishes
+      const size_t part_stride4 = tail_tile_elems / 4;   // float4 per partial tile
+      float4* const tile_regions = reinterpret_cast<float4*>(p.tail_ws + static_cast<size_t>(w.tail_index) * p.tail_parts * tail_tile_elems + warp_slab) + lane;
+      uint32_t* const tile_flags = p.tail_flags + static_cast<size_t>(w.tail_index) * p.tail_parts * (CG * 4) + flag_lane;
+      if (tail_item) {
+        const int slice = BN / p.tail_parts;  // a multiple of 32 (the plan sees to it)
+        lo = w.part * slice;
+        hi = slab_ok ? lo + slice : lo;
+        if (exchange) {
+          float4* const mine = tile_regions + static_cast<size_t>(w.part) * part_stride4;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            if ((c >= lo && c < lo + slice) || n_blk * BN + c >= p.N) continue;  // own slice, or beyond the matrix
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(c), v);
+            tmem_ld_wait();
+            float4* wdst = mine + static_cast<size_t>(c) * 8u;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + static_cast<size_t>(c_begin) * 8u + j * 32);
+            for (int j = 0; j < 8; ++j) {
+              wdst[j * 32] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                         __uint_as_float(v[4 * j + 3]));
+            }
+          }
+          // Publish: every lane's stores are ordered before the flag the other parts poll.
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) st_release_gpu(tile_flags + static_cast<size_t>(w.part) * (CG * 4), p.epoch);
+          for (int q = 0; q < p.tail_parts; ++q) {
+            if (q == w.part) continue;
+            if (!wait_flag(tile_flags + static_cast<size_t>(q) * (CG * 4), p.epoch, waiter, tile)) {
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+        }
+      }
+      // This lane's float4 column of the first other part's partial tile; its first chunk is loaded now.
+      const int first_other = w.part == 0 ? 1 : 0;
+      const float4* tail_src = tile_regions + static_cast<size_t>(first_other) * part_stride4;
+      float4 ahead[8];
+      if (tail_item && exchange && lo < hi) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + static_cast<size_t>(lo) * 8u + j * 32);
       }
       // One 32-column chunk of this warp's rows per iteration.  (Keeping the next chunk's TMEM
       // load in flight during the current one costs 32 more live registers, which the compiler
       // could only find by spilling -- not an option for registers that an asynchronous load is
       // still writing.)
 #pragma unroll 1
-      for (int c = c_begin; c < (slab_ok ? c_end : c_begin); c += 32) {
+      for (int c = lo; c < hi; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(c), v);
         tmem_ld_wait();
@@ -772,25 +805,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           continue;
         }
-        if (w.part > 0) {
-          // Contributor: hand the raw fp32 tile to the owner (whole rows, ragged edges included).
-          float4* wdst = reinterpret_cast<float4*>(p.tail_ws + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (w.part - 1)) * tail_tile_elems +
-                                                   warp_slab + static_cast<size_t>(c) * 32u) + lane;
-          if (exchange) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) wdst[j * 32] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
-          }
-          continue;
-        }
         if (p.acc_int == 2) {
           // Integer sums (never part of a K split: the plan refuses it) are moved, not converted:
           // C receives the s32 words bit for bit.
           if (row_ok) store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid);
           continue;
         }
-        if (w.part == 0 && exchange) {
-          // The first contributor's chunk was fetched one iteration ahead (`ahead`); further
-          // contributors, if any, are read in place.
+        if (tail_item && exchange) {
+          // The first other part's chunk was fetched one iteration ahead (`ahead`); further
+          // parts, if any, are read in place, in increasing part order.
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             x[4 * j] += ahead[j].x;
@@ -798,13 +821,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             x[4 * j + 2] += ahead[j].z;
             x[4 * j + 3] += ahead[j].w;
           }
-          if (c + 32 < c_end) {
+          if (c + 32 < hi) {
             const float4* nxt = tail_src + static_cast<size_t>(c + 32) * 8u;
 #pragma unroll
             for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(nxt + j * 32);
           }
-          for (int q = 2; q < p.tail_parts; ++q) {
-            const float4* src = tail_src + static_cast<size_t>(q - 1) * (tail_tile_elems / 4) + static_cast<size_t>(c) * 8u;
+          for (int q = first_other + 1; q < p.tail_parts; ++q) {
+            if (q == w.part) continue;
+            const float4* src = tile_regions + static_cast<size_t>(q) * part_stride4 + static_cast<size_t>(c) * 8u;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const float4 t = __ldcg(src + j * 32);
@@ -832,15 +856,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (row_ok && (p.debug_mode & 32) == 0) {
           store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
-        }
-      }
-      if (w.part > 0 && exchange) {
-        // Publish: every lane's stores are ordered before the flag the owner polls.
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-          uint32_t* flag = p.tail_flags + (static_cast<size_t>(w.tail_index) * (p.tail_parts - 1) + (w.part - 1)) * (CG * 4) + flag_lane;
-          st_release_gpu(flag, p.epoch);
         }
       }
       tc_fence_before_sync();

@@ -293,27 +293,25 @@ void plan_tail_split(b200_gemm_plan* plan) {
   if (units < 2 || tiles < 1) return;
   const int tail = tiles % units;  // tiles < units: every tile is a tail tile
   if (tail == 0) return;
-  int parts = units / tail;
-  if (parts > 8) parts = 8;
+  // Parts: a power of two (each part finishes BN / parts columns, a multiple of 32) that the idle
+  // units can host, with at least four K blocks each and no empty part.
+  int parts = 0;
+  for (int cand = 8; cand >= 2; cand /= 2) {
+    if (cand > units / tail || plan->bn / cand < 32 || plan->num_kb / cand < 4) continue;
+    const int per = (plan->num_kb + cand - 1) / cand;
+    if ((plan->num_kb + per - 1) / per != cand) continue;
+    parts = cand;
+    break;
+  }
   if (parts < 2) return;
-  while (parts >= 2 && plan->num_kb / parts < 4) --parts;
-  if (parts < 2) return;
-  // The owner (part 0) takes a few more K blocks than the contributors, so that their partial
-  // tiles are already in the workspace when the owner's own MMAs finish.
-  int kb0 = (plan->num_kb + parts - 1) / parts + 5;  // measured: 0..3 and 8 are slower on the large and the skinny shapes
-  if (kb0 > plan->num_kb - (parts - 1)) kb0 = plan->num_kb - (parts - 1);
-  const int rest = plan->num_kb - kb0;
-  const int tail_kb = (rest + parts - 2) / (parts - 1);
-  parts = 1 + (rest + tail_kb - 1) / tail_kb;
-  if (parts < 2) return;
+  const int tail_kb = (plan->num_kb + parts - 1) / parts;
   plan->tail_tiles = tail;
   plan->tail_parts = parts;
-  plan->tail_kb0 = kb0;
+  plan->tail_kb0 = tail_kb;
   plan->tail_kb = tail_kb;
-  const int64_t flags = static_cast<int64_t>(tail) * (parts - 1) * plan->cg * gemm::kEpilogueWarps * sizeof(uint32_t);
+  const int64_t flags = static_cast<int64_t>(tail) * parts * plan->cg * gemm::kEpilogueWarps * sizeof(uint32_t);
   plan->tail_flag_bytes = (flags + 255) / 256 * 256;
-  plan->tail_ws_bytes = plan->tail_flag_bytes +
-                        static_cast<int64_t>(tail) * (parts - 1) * (gemm::kBM * plan->cg) * plan->bn * sizeof(float);
+  plan->tail_ws_bytes = plan->tail_flag_bytes + static_cast<int64_t>(tail) * parts * (gemm::kBM * plan->cg) * plan->bn * sizeof(float);
 }
 
 // Persistent grid: one CTA (pair) per work item up to `units_cap`.
