@@ -637,7 +637,9 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
 # DRAM bytes (read + write) per launch of the dominant kernel from the ncu captures summarised
 # under profiles/ (null where no capture exists for the workload).
 TRAFFIC_BYTES: dict = {
-    "bf16_4096": 99.4e6,  # ncu capture summarised under profiles/: 85.4 MB read + 14.0 MB written per launch
+    # per-launch dram__bytes_read.sum + dram__bytes_write.sum of the ncu captures summarised under profiles/
+    "bf16_4096": 107.2e6,  # 87.6 MB read + 19.5 MB written (the surplus over 100.7 MB is the tail-split exchange)
+    "decode_16": 138.5e6,  # 134.55 MB read + 3.95 MB written
 }
 
 
