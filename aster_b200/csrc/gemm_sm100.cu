@@ -294,10 +294,14 @@ void plan_tail_split(b200_gemm_plan* plan) {
   const int tail = tiles % units;  // tiles < units: every tile is a tail tile
   if (tail == 0) return;
   // Parts: a power of two (each part finishes BN / parts columns, a multiple of 32) that the idle
-  // units can host, with at least four K blocks each and no empty part.
+  // units can host, with no empty part and enough K blocks each to pay for the exchange: it costs
+  // 3-5 us (export, fence, flag, read back), a K block of a full-width tile about 0.36 us, so a
+  // split that saves fewer than ~12 K blocks per unit makes the launch longer (512^3: 8 K blocks,
+  // 9.3 -> 6 us per launch without the split).
+  constexpr int kMinKbPerPart = 12;
   int parts = 0;
   for (int cand = 8; cand >= 2; cand /= 2) {
-    if (cand > units / tail || plan->bn / cand < 32 || plan->num_kb / cand < 4) continue;
+    if (cand > units / tail || plan->bn / cand < 32 || plan->num_kb / cand < kMinKbPerPart) continue;
     const int per = (plan->num_kb + cand - 1) / cand;
     if ((plan->num_kb + per - 1) / per != cand) continue;
     parts = cand;

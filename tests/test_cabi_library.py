@@ -98,9 +98,11 @@ def test_plan_resources_without_a_gpu(native_lib):
     assert r.smem_bytes <= 232448 and r.ctas_per_sm == 1 and r.workspace_bytes == 0 and r.packed_b_bytes == 0
     p.destroy()
     p.destroy()  # idempotent
-    small = GemmPlan(512, 512, 512).resources()
+    small = GemmPlan(512, 512, 2048).resources()
     assert small.tile_n == 64 and small.num_tiles == 16 and small.cta_group == 2
     assert (small.tail_tiles, small.tail_parts, small.grid_ctas) == (16, 2, 64) and small.optional_workspace_bytes > 0
+    short = GemmPlan(512, 512, 512).resources()  # too few K blocks to pay for the exchange
+    assert (short.tail_parts, short.grid_ctas, short.optional_workspace_bytes) == (0, 32, 0)
     assert (r.tail_tiles, r.tail_parts) == (34, 2) and r.optional_workspace_bytes == 34 * (256 * 256 * 4 + 32) + 0 * 256 or r.optional_workspace_bytes > 34 * 256 * 256 * 4
     assert GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources().tail_parts == 0
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()

@@ -241,12 +241,12 @@ class TestTailSplit:
     """The last, partly filled round of tiles cut along K when the caller lends the workspace."""
 
     @pytest.mark.parametrize("shape,kw", [
-        ((4096, 4096, 1024), {}),                                   # 256 tiles on 74 pairs: 34 tail tiles x 2 parts
-        ((1024, 1024, 2048), dict(tile_n=256)),                     # 16 tiles, all tail: 4 parts
-        ((512, 512, 512), {}),                                      # 16 small tiles x 2 parts
+        ((4096, 4096, 2048), {}),                                   # 256 tiles on 74 pairs: 34 tail tiles x 2 parts
+        ((1024, 1024, 4096), dict(tile_n=256)),                     # 16 tiles, all tail: 4 parts
+        ((512, 512, 2048), {}),                                     # 16 small tiles x 2 parts
         ((1280, 512, 4096), dict(tile_n=128, max_ctas=16)),         # 20 tiles on 8 pairs: 4 tail tiles x 2 parts
-        ((640, 512, 2048), dict(cta_group=1, tile_n=128, max_ctas=16)),  # single CTAs: 20 tiles on 16 CTAs -> 4 tail x 4 parts
-        ((300, 200, 1032), dict(tile_n=64)),                        # ragged edges in the exchanged tiles
+        ((640, 512, 4096), dict(cta_group=1, tile_n=128, max_ctas=16)),  # single CTAs: 20 tiles on 16 CTAs -> 4 tail x 4 parts
+        ((300, 200, 2056), dict(tile_n=64)),                        # ragged edges in the exchanged tiles
     ])
     @pytest.mark.parametrize("dtype_c", ["f32", "bf16"])
     def test_against_oracle(self, gpu, shape, kw, dtype_c):
@@ -258,6 +258,11 @@ class TestTailSplit:
     def test_epilogue_and_fp8(self, gpu):
         run(1024, 1024, 2048, "bf16", "bf16", "normal", 2, bias=True, relu=True, tail_split=True, tile_n=256)
         run(1024, 1024, 4096, "e4m3", "bf16", "normal", 3, tail_split=True, tile_n=256)
+
+    def test_short_k_is_not_split(self, gpu):
+        # the exchange costs more than a few K blocks save: such plans keep whole tiles
+        assert GemmPlan(512, 512, 512, "bf16", "bf16").resources().tail_parts == 0
+        assert GemmPlan(512, 512, 2048, "bf16", "bf16").resources().tail_parts == 2
 
     def test_repeated_launches_reuse_the_workspace(self, gpu):
         from aster_b200.execution import GpuBuffer

@@ -187,7 +187,7 @@ class TestBlockScaledFp8:
         assert noise < (0.08 if elem == "e4m3" else 0.16)
 
     def test_epilogue_split_k_and_tail_split(self, gpu):
-        M, N, K = 384, 256, 2048
+        M, N, K = 384, 256, 4096
         _, _, qa, sa, qb, sb = mx_inputs(M, N, K, seed=4, spread=False)
         bias = np.random.default_rng(5).standard_normal(N).astype(np.float32)
         want = np.maximum(orc.gemm_mx(qa, qb, sa, sb) + bias[None, :], 0)
