@@ -449,9 +449,10 @@ def run_gemm(args, job: Job, w: dict, name: str) -> dict:
             raw.free()
         plan.set_mx_scales(small["block_scales_a"], small["block_scales_b"])
 
+    bound = [plan.bind(dA, dB, dC, small.get("bias"), small.get("scale_a"), small.get("scale_b"), ws) for dA, dB, dC in sets]
+
     def run_step(i):
-        dA, dB, dC = sets[i % n_sets]
-        plan.run(dA, dB, dC, small.get("bias"), small.get("scale_a"), small.get("scale_b"), ws)
+        bound[i % n_sets]()
 
     sampler = ClockSampler(job.local_rank)
     sampler.start()

@@ -458,6 +458,31 @@ class TestPlanObject:
         for b in bufs:
             b.free()
 
+    def test_bound_launch_equals_run(self, gpu):
+        from aster_b200 import _native as nat
+        from aster_b200.execution import GpuBuffer
+
+        inp = orc.make_inputs(256, 384, 512, "bf16", "uniform", 9)
+        plan = GemmPlan(256, 384, 512, "bf16", "f32")
+        dA, dB = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes)
+        dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
+        outs = []
+        for use_bind in (False, True):
+            dC = GpuBuffer(256 * 384 * 4)
+            dC.zero()
+            if use_bind:
+                launch = plan.bind(dA, dB, dC)
+                launch()
+                launch()  # reusable
+            else:
+                plan.run(dA, dB, dC)
+            nat.call("b200_device_synchronize")
+            out = np.empty((256, 384), np.float32)
+            dC.copy_to_host(out)
+            outs.append(out)
+        assert np.array_equal(outs[0], outs[1])
+        check(outs[1], inp, "bf16", "f32")
+
 
 class TestDependentLaunch:
     """Launches use programmatic stream serialisation: a kernel may set itself up, and with
