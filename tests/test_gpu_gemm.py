@@ -458,6 +458,35 @@ class TestPlanObject:
         for b in bufs:
             b.free()
 
+    def test_milestone_timeline(self, gpu):
+        """The bring-up timeline: every CTA's stamps are in causal order and within the launch."""
+        from aster_b200 import _native as nat
+        from aster_b200.execution import GpuBuffer
+
+        plan = GemmPlan(1024, 1024, 2048, "bf16", "bf16", no_tail_split=True)
+        grid = plan.resources().grid_ctas
+        bufs = [GpuBuffer(n) for n in (1024 * 2048 * 2, 1024 * 2048 * 2, 1024 * 1024 * 2)]
+        for b in bufs:
+            b.zero()
+        tl = GpuBuffer(grid * 16 * 8)
+        tl.zero()
+        nat.call("b200_gemm_debug_timeline", plan.handle, tl.ptr)
+        plan.run(*bufs)
+        nat.call("b200_device_synchronize")
+        nat.call("b200_gemm_debug_timeline", plan.handle, None)
+        t = np.zeros((grid, 16), np.uint64)
+        tl.copy_to_host(t)
+        t = t.astype(np.int64)
+        leaders = t[::plan.resources().cta_group]
+        for a, b in ((0, 1), (1, 2), (2, 3), (3, 4), (4, 5), (5, 6), (6, 7), (7, 8)):
+            assert (leaders[:, a] <= leaders[:, b]).all(), (a, b)
+        assert (t[:, 0] > 0).all() and (t[:, 8] - t[:, 0]).max() < 5_000_000  # ns
+        plan.run(*bufs)  # detached: launches no longer write the buffer
+        nat.call("b200_device_synchronize")
+        again = np.zeros((grid, 16), np.uint64)
+        tl.copy_to_host(again)
+        assert np.array_equal(again.astype(np.int64), t)
+
     def test_bound_launch_equals_run(self, gpu):
         from aster_b200 import _native as nat
         from aster_b200.execution import GpuBuffer
