@@ -30,8 +30,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("label", nargs="?", help="config label (reference grammar, optional _b200_ suffix)")
     ap.add_argument("--size", type=parse_mnk, help="MxNxK when no label is given")
-    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "e4m3"])
-    ap.add_argument("--out-dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "e4m3", "e5m2", "i8"])
+    ap.add_argument("--out-dtype", default="f32", choices=["f32", "bf16", "i32"])
     ap.add_argument("--epilogue", default="none", choices=["none", "bias_relu", "bias", "relu"])
     ap.add_argument("--direct-b", action="store_true", help="B preshuffled as in the reference's direct-B path")
     ap.add_argument("--iterations", type=int, default=NUM_ITERATIONS)

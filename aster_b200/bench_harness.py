@@ -34,7 +34,7 @@ def peak_tflops_f16(mcpu: str) -> float:
 
 
 def peak_tflops(mcpu: str, dtype_ab: str = "f16") -> float:
-    return _PEAK_TFLOPS_FP8_BY_MCPU[mcpu] if dtype_ab == "e4m3" else _PEAK_TFLOPS_F16_BY_MCPU[mcpu]
+    return _PEAK_TFLOPS_FP8_BY_MCPU[mcpu] if dtype_ab in ("e4m3", "e5m2", "i8") else _PEAK_TFLOPS_F16_BY_MCPU[mcpu]
 
 
 class InitMode(enum.StrEnum):
@@ -79,7 +79,8 @@ def init_array(shape, mode: InitMode, role: str, dtype=np.float16, seed: int = 4
 
 def make_inputs(cfg, init_mode: InitMode = INIT_DEFAULT, seed: int = 42):
     """A and B for ``cfg`` in its storage type.  Returns ``(A, B)`` for 16-bit configs and
-    ``(A, B, scale_a, scale_b)`` for e4m3 (per-tensor ``amax/448`` quantisation)."""
+    ``(A, B, scale_a, scale_b)`` for e4m3 (per-tensor ``amax/448`` quantisation); int8 operands
+    are scaled to the full integer range."""
     a = init_array(cfg.spec.operand_shape(Operand.A), init_mode, "A", dtype=np.float32, seed=seed)
     b = init_array(cfg.spec.operand_shape(Operand.B), init_mode, "B", dtype=np.float32, seed=seed)
     dt = getattr(cfg, "dtype_ab", "f16")
@@ -87,6 +88,8 @@ def make_inputs(cfg, init_mode: InitMode = INIT_DEFAULT, seed: int = 42):
         qa, sa = quantize_e4m3(a)
         qb, sb = quantize_e4m3(b)
         return qa, qb, float(sa), float(sb)
+    if dt == "i8":  # spread the values over the whole integer range
+        a, b = (x * (127.0 / max(float(np.abs(x).max()), 1e-30)) for x in (a, b))
     return from_f32(a, dt), from_f32(b, dt)
 
 

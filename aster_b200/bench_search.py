@@ -171,7 +171,7 @@ def parse_mnk(text: str) -> tuple:
 
 def b200_gemm_grid(M: int, N: int, K: int, dtype_ab: str = "bf16", dtype_c: str = "bf16", epilogue: str = "none") -> SweepGrid:
     """The plan knobs worth sweeping on B200 for one problem size."""
-    kb_elems = 128 if dtype_ab == "e4m3" else 64
+    kb_elems = 128 if dtype_ab in ("e4m3", "e5m2", "i8") else 64
     k_blocks = -(-K // kb_elems)
 
     def stage_bytes(d):
@@ -241,8 +241,8 @@ def run_sweep(instances: list, *, iterations: int = NUM_ITERATIONS, results_stre
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--size", type=parse_mnk, required=True)
-    ap.add_argument("--dtype", default="bf16", choices=["f16", "bf16", "e4m3"])
-    ap.add_argument("--out-dtype", default="bf16", choices=["f32", "bf16"])
+    ap.add_argument("--dtype", default="bf16", choices=["f16", "bf16", "e4m3", "e5m2", "i8"])
+    ap.add_argument("--out-dtype", default="bf16", choices=["f32", "bf16", "i32"])
     ap.add_argument("--iterations", type=int, default=60)
     ap.add_argument("--sample", type=int, default=0, help="0 = every eligible config")
     ap.add_argument("--verify-top", type=int, default=3)
@@ -259,7 +259,7 @@ def main(argv=None) -> int:
     try:
         # fp8 results get their own registry slot: the size key alone would make them compete
         # with the 16-bit configs of the same shape
-        bench = BENCH_HOOKS["bench_label"] + ("_fp8" if args.dtype == "e4m3" else "")
+        bench = BENCH_HOOKS["bench_label"] + {"e4m3": "_fp8", "e5m2": "_bf8", "i8": "_i8"}.get(args.dtype, "")
         ranked = run_sweep(instances, iterations=args.iterations, results_stream=stream, verify_top=args.verify_top, bench=bench)
     finally:
         if args.results_file:
