@@ -38,7 +38,7 @@ namespace gemm {
 constexpr int kBM = 128;             // rows per CTA tile = TMEM lanes
 constexpr int kRowBytes = 128;       // bytes of K per stage row (one swizzle span)
 constexpr int kMmasPerStage = 4;     // 128 B / 32 B consumed per tcgen05.mma
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 16;
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
@@ -118,14 +118,19 @@ __device__ __forceinline__ void stamp(const Params& p, int slot) {
 // the next stage stays 1024-byte aligned.
 constexpr int kScaleBlockBytes = 512;  // 128 rows x 4 K blocks of 32
 __host__ __device__ constexpr int scale_stage_bytes(int bn) { return (kScaleBlockBytes * (1 + bn / 128) + 1023) / 1024 * 1024; }
-__host__ __device__ constexpr int stage_bytes(int bn, int cg = 1, bool mx = false) {
-  return (kBM + bn / cg) * kRowBytes + (mx ? scale_stage_bytes(bn) : 0);
+// `am` = rows of A that a stage holds: 128, or 32 / 64 for skinny problems (M <= am), whose
+// stages then spend their bytes on B.  The MMA still reads 128 rows from the stage's start; the
+// rows beyond `am` are whatever follows in shared memory and only reach accumulator rows that no
+// one reads (rows >= M are never loaded from TMEM or stored).
+__host__ __device__ constexpr int stage_bytes(int bn, int cg = 1, bool mx = false, int am = kBM) {
+  return (am + bn / cg) * kRowBytes + (mx ? scale_stage_bytes(bn) : 0);
 }
-// Barrier block that follows the stage ring: full[8], empty[8], acc_full[2], acc_empty[2],
-// drain, TMEM base slot, abort flag.
-constexpr int kBarrierBytes = 256;
-__host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1, bool mx = false) {
-  return stages * stage_bytes(bn, cg, mx) + kBarrierBytes + 1024;
+// Barrier block that follows the stage ring (and, for am < 128, the slack that the last stage's
+// 128-row A read runs into): full[16], empty[16], acc_full[2], acc_empty[2], drain, TMEM base
+// slot, abort flag.
+constexpr int kBarrierBytes = 384;
+__host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1, bool mx = false, int am = kBM) {
+  return stages * stage_bytes(bn, cg, mx, am) + (kBM - am) * kRowBytes + kBarrierBytes + 1024;
 }
 // Two accumulators of bn columns; a block-scaled kernel adds two sets of 16 scale columns.
 constexpr int kScaleTmemCols = 16;
@@ -377,7 +382,7 @@ __device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], boo
 // rings in the same shared memory.  In the pair, full[] lives in the leader and counts the
 // bytes of both CTAs' copies; empty[] and acc_full[] exist in both CTAs and the leader's
 // commits arrive on each; acc_empty[] lives in the leader and collects both CTAs' epilogues.
-template <int BN, typename OutT, int CG, bool MX = false>
+template <int BN, typename OutT, int CG, bool MX = false, int AM = kBM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const Params p) {
@@ -386,9 +391,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair");
   constexpr uint32_t kBRows = BN / CG;  // B rows staged by this CTA
-  constexpr uint32_t kABytes = kBM * kRowBytes;
+  static_assert(AM == kBM || (CG == 1 && !MX && (AM == 32 || AM == 64)), "short A stages: one CTA, plain operands, 32 or 64 rows");
+  constexpr uint32_t kABytes = AM * kRowBytes;
   constexpr uint32_t kBBytes = kBRows * kRowBytes;
-  constexpr uint32_t kStageBytes = stage_bytes(BN, CG, MX);
+  constexpr uint32_t kStageBytes = stage_bytes(BN, CG, MX, AM);
   constexpr uint32_t kLoadBytes = kABytes + kBBytes + (MX ? kScaleBlockBytes * (1 + BN / 128) : 0);  // bytes one CTA copies per stage
   constexpr uint32_t kTmemCols = tmem_columns(BN, MX);
   // Block-scaled tiles of 256 columns keep a single accumulator: two of them would fill the
@@ -402,16 +408,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_raw_u32 = smem_u32(smem_raw);
   const uint32_t smem_base = (smem_raw_u32 + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-  const uint32_t bar_base = smem_base + static_cast<uint32_t>(p.stages) * kStageBytes;
+  const uint32_t bar_base = smem_base + static_cast<uint32_t>(p.stages) * kStageBytes + (kBM - AM) * kRowBytes;
   uint8_t* bar_ptr = smem_raw + (bar_base - smem_raw_u32);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
-  auto acc_full_bar = [&](int a) { return bar_base + 128u + 8u * a; };
-  auto acc_empty_bar = [&](int a) { return bar_base + 144u + 8u * a; };
-  const uint32_t drain_bar = bar_base + 160u;
-  const uint32_t tmem_slot = bar_base + 168u;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_ptr + 168);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_ptr + 172);
+  auto empty_bar = [&](int s) { return bar_base + 128u + 8u * s; };
+  auto acc_full_bar = [&](int a) { return bar_base + 256u + 8u * a; };
+  auto acc_empty_bar = [&](int a) { return bar_base + 272u + 8u * a; };
+  const uint32_t drain_bar = bar_base + 288u;
+  const uint32_t tmem_slot = bar_base + 296u;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_ptr + 296);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_ptr + 300);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

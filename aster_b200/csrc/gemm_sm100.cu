@@ -97,8 +97,18 @@ KernelFn select_kernel_cg(int bn, bool f32) {
   }
 }
 
-KernelFn select_kernel(int bn, int dtype_c, int cta_group, bool mx) {
+// Short-A variants (skinny M): one CTA per tile, 64- or 128-column tiles.
+template <int AM>
+KernelFn select_kernel_short_a(int bn, bool f32) {
+  if (bn == 64) return f32 ? gemm::gemm_tn_kernel<64, float, 1, false, AM> : gemm::gemm_tn_kernel<64, __nv_bfloat16, 1, false, AM>;
+  if (bn == 128) return f32 ? gemm::gemm_tn_kernel<128, float, 1, false, AM> : gemm::gemm_tn_kernel<128, __nv_bfloat16, 1, false, AM>;
+  return nullptr;
+}
+
+KernelFn select_kernel(int bn, int dtype_c, int cta_group, bool mx, int am) {
   const bool f32 = dtype_c == B200_F32 || dtype_c == B200_I32;  // 32-bit outputs share the store path
+  if (am == 32) return select_kernel_short_a<32>(bn, f32);
+  if (am == 64) return select_kernel_short_a<64>(bn, f32);
   if (mx) {
     if (cta_group == 2) {
       if (bn == 256) return f32 ? gemm::gemm_tn_kernel<256, float, 2, true> : gemm::gemm_tn_kernel<256, __nv_bfloat16, 2, true>;
@@ -237,6 +247,7 @@ struct b200_gemm_plan {
   b200_gemm_desc desc;
   int bn = 0;
   int cg = 1;         // CTAs per MMA: 1, or 2 for a CTA pair (cluster of two)
+  int am = gemm::kBM; // rows of A per stage: 128, or 32 / 64 for skinny M (see gemm::stage_bytes)
   bool mx = false;    // block-scaled 8-bit floats: scales come from b200_gemm_plan_set_mx_scales
   const void* sfa = nullptr;
   const void* sfb = nullptr;
@@ -411,7 +422,7 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   B200_REQUIRE(!plan->mx || (plan->sfa != nullptr && plan->sfb != nullptr),
                "gemm_run: a block-scaled plan needs its scales first (b200_gemm_plan_set_mx_scales)");
   if (plan->map_a_ptr != A) {
-    int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), gemm::kBM);  // per CTA
+    int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), static_cast<uint32_t>(plan->am));  // per CTA
     if (rc != B200_OK) return rc;
     plan->map_a_ptr = A;
   }
@@ -617,20 +628,27 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   plan->num_kb = ceil_div(k_blocks, split);
   plan->total_kb = plan->num_kb * split;
 
-  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024) / gemm::stage_bytes(bn, cg, mx);
-  int stages = d.stages > 0 ? d.stages : (max_stages < gemm::kMaxStages ? max_stages : gemm::kMaxStages);
+  // Skinny M (at most 64 rows, one CTA per tile): stage only 32 or 64 rows of A, so that the
+  // ring holds more of B, the operand that such a problem streams from HBM.  tile_m = 128
+  // asks for full A stages.
+  int am = gemm::kBM;
+  if (cg == 1 && !mx && d.tile_m == 0 && d.M <= 64 && (bn == 64 || bn == 128)) am = d.M <= 32 ? 32 : 64;
+  plan->am = am;
+  const int stage_cap = am < gemm::kBM ? gemm::kMaxStages : 8;  // full-A stages never profit from more than 8 slots
+  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024 - (gemm::kBM - am) * gemm::kRowBytes) / gemm::stage_bytes(bn, cg, mx, am);
+  int stages = d.stages > 0 ? d.stages : (max_stages < stage_cap ? max_stages : stage_cap);
   if (stages > max_stages) {
     delete plan;
     return b200::fail(B200_ERR_INVALID, "gemm_plan_create: %d stages of %d bytes exceed the %d-byte shared memory limit", stages,
-                      gemm::stage_bytes(bn, cg, mx), kMaxSmemOptin);
+                      gemm::stage_bytes(bn, cg, mx, am), kMaxSmemOptin);
   }
   plan->stages = stages;
-  plan->smem = gemm::smem_bytes(bn, stages, cg, mx);
+  plan->smem = gemm::smem_bytes(bn, stages, cg, mx, am);
   // Two resident CTAs would both ask for TMEM; keep the footprint above half the SM's shared
   // memory whenever two allocations (2 * tmem_columns) would not fit in the 512 columns.
   if (2 * gemm::tmem_columns(bn, mx) > 512 && plan->smem <= kMaxSmemOptin / 2) plan->smem = kMaxSmemOptin / 2 + 1024;
   plan->raster_group = d.raster_group > 0 ? d.raster_group : 8;
-  plan->kernel = select_kernel(bn, d.dtype_c, cg, mx);
+  plan->kernel = select_kernel(bn, d.dtype_c, cg, mx, am);
   const int cap = d.max_ctas > 0 ? d.max_ctas : kDefaultSms;
   size_grid(plan, cg == 2 ? (cap / 2 < 1 ? 1 : cap / 2) : cap);
   *out = plan;

@@ -558,3 +558,29 @@ class TestDependentLaunch:
         assert np.array_equal(plain, early[0]) and np.array_equal(plain, early[1])
         no_pdl = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", debug_mode=16, **kw)
         assert np.array_equal(plain, no_pdl)
+
+
+class TestSkinnyM:
+    """M <= 64: stages hold only 32 or 64 rows of A (more ring slots for B).  Same MMAs in the
+    same order as with full A stages, so the results are bit-identical to ``tile_m=128``."""
+
+    @pytest.mark.parametrize("M", [1, 8, 16, 32, 33, 48, 64])
+    @pytest.mark.parametrize("kw", [dict(tile_n=64), dict(tile_n=128), dict(tile_n=128, tail_split=True), dict(tile_n=64, split_k=2),
+                                    dict(tile_n=64, b_layout="packed")])
+    def test_equals_full_a_stages_bitwise(self, gpu, M, kw):
+        N, K = 1024, 4096
+        inp = orc.make_inputs(M, N, K, "bf16", "uniform", 4)
+        short = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", **kw)
+        full = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", tile_m=128, **kw)
+        assert np.array_equal(short, full)
+        check(short, inp, "bf16", "bf16")
+
+    def test_deep_rings_and_other_types(self, gpu):
+        plan = GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64)
+        assert plan.resources().stages == 16 and GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64, tile_m=128).resources().stages <= 8
+        run(16, 2048, 8192, "bf16", "f32", "uniform", 4, tile_n=64, bias=True, relu=True)
+        run(24, 1000, 2064, "f16", "f32", "normal", 5, tile_n=64)            # ragged N, K not a multiple of the stage
+        run(40, 512, 4096, "e4m3", "bf16", "normal", 3, tile_n=128)
+        ia = np.random.default_rng(1).integers(-128, 128, (16, 2048), dtype=np.int8)
+        ib = np.random.default_rng(2).integers(-128, 128, (512, 2048), dtype=np.int8)
+        assert np.array_equal(gemm(ia, ib, dtype_ab="i8", dtype_c="i32", tile_n=64), orc.gemm_i32(ia, ib))
