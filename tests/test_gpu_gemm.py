@@ -550,7 +550,8 @@ class TestDependentLaunch:
         assert all(np.array_equal(h1, r[0]) and np.array_equal(h2, r[1]) for r in results[1:])
 
     @pytest.mark.parametrize("shape,kw", [((16, 1024, 4096), dict(tile_n=128, tail_split=True)), ((512, 512, 1024), {}),
-                                           ((300, 200, 520), dict(cta_group=1, b_layout="packed"))])
+                                           ((300, 200, 520), dict(cta_group=1, b_layout="packed")),
+                                           ((48, 200, 1000), dict(split_k=3, tile_n=64)), ((2048, 1024, 512), dict(stages=3))])
     def test_static_b_does_not_change_results(self, gpu, shape, kw):
         inp = orc.make_inputs(*shape, "bf16", "uniform", 6)
         plain = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", **kw)

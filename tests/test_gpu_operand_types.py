@@ -194,7 +194,8 @@ class TestBlockScaledFp8:
         kw = dict(dtype_ab="mxe4m3", dtype_c="f32", block_scales_a=sa, block_scales_b=sb, bias=bias, relu=True)
         for extra in ({}, {"split_k": 3}, {"max_ctas": 4, "tail_split": True}, {"stages": 2}, {"tile_n": 256}, {"tile_n": 256, "max_ctas": 2},
                       {"tile_n": 256, "split_k": 2, "stages": 3}, {"cta_group": 1}, {"cta_group": 1, "tile_n": 128, "max_ctas": 3, "tail_split": True},
-                      {"cta_group": 2, "tile_n": 128, "split_k": 2}, {"cta_group": 2, "tile_n": 256, "max_ctas": 2, "tail_split": True}):
+                      {"cta_group": 2, "tile_n": 128, "split_k": 2}, {"cta_group": 2, "tile_n": 256, "max_ctas": 2, "tail_split": True},
+                      {"static_b": True}, {"static_b": True, "cta_group": 1, "stages": 2}):
             assert orc.rel_frobenius(gemm(qa, qb, **kw, **extra), want) <= 1e-3, extra
 
     def test_refusals(self, gpu):
