@@ -294,14 +294,19 @@ __device__ __forceinline__ WorkItem decode_item(const Params& p, int item) {
     w.nkb = p.num_kb;
     return w;
   }
-  const int whole = p.tail_parts > 1 ? p.num_tiles - p.tail_tiles : p.num_tiles;
-  if (item < whole) {
-    w.tile = item;
+  // The split tiles come FIRST: their parts start together on neighbouring units, and the
+  // exchange of partial sums (flags, L2 round trips) then runs in the epilogue warps while the
+  // units' MMA warps are already on their next, whole tiles.  Scheduled last, the same exchange
+  // sat exposed at the end of the launch.
+  const int tail_items = p.tail_parts > 1 ? p.tail_tiles * p.tail_parts : 0;
+  const int whole = p.num_tiles - (p.tail_parts > 1 ? p.tail_tiles : 0);
+  if (item >= tail_items) {
+    w.tile = item - tail_items;
     w.kb0 = 0;
     w.nkb = p.num_kb;
     return w;
   }
-  const int t = item - whole;
+  const int t = item;
   w.tail_index = t / p.tail_parts;
   w.part = t - w.tail_index * p.tail_parts;
   w.tile = whole + w.tail_index;
