@@ -65,7 +65,7 @@ def test_version_and_error_text(native_lib):
     (dict(M=512, N=64, K=64, tile_m=128, cta_group=2), "contradicts"),
     (dict(M=512, N=64, K=64, cta_group=2, tile_n=32), "tile_n >= 64"),
     (dict(M=512, N=64, K=64, cta_group=2, b_layout="packed"), "cta_group=1"),
-    (dict(M=64, N=64, K=64, stages=9), "stages=9"),
+    (dict(M=64, N=64, K=64, stages=17), "stages=17"),
     (dict(M=64, N=64, K=64, tile_n=256, stages=5), "shared memory limit"),
     (dict(M=512, N=512, K=64, tile_n=256, stages=8, cta_group=2), "shared memory limit"),
     (dict(M=64, N=64, K=64, cta_group=3), "cta_group=3"),
@@ -101,8 +101,9 @@ def test_plan_resources_without_a_gpu(native_lib):
     small = GemmPlan(512, 512, 2048).resources()
     assert small.tile_n == 64 and small.num_tiles == 16 and small.cta_group == 2
     assert (small.tail_tiles, small.tail_parts, small.grid_ctas) == (16, 2, 64) and small.optional_workspace_bytes > 0
-    short = GemmPlan(512, 512, 512).resources()  # too few K blocks to pay for the exchange
-    assert (short.tail_parts, short.grid_ctas, short.optional_workspace_bytes) == (0, 32, 0)
+    short = GemmPlan(512, 512, 512).resources()  # too few K blocks to pay for the exchange; small single-CTA tiles for latency
+    assert (short.tail_parts, short.optional_workspace_bytes) == (0, 0)
+    assert (short.cta_group, short.tile_n, short.grid_ctas) == (1, 32, 64)
     assert (r.tail_tiles, r.tail_parts) == (34, 2) and r.optional_workspace_bytes == 34 * (256 * 256 * 4 + 32) + 0 * 256 or r.optional_workspace_bytes > 34 * 256 * 256 * 4
     assert GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources().tail_parts == 0
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()
