@@ -705,6 +705,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
     OutT* const C = static_cast<OutT*>(p.C);
     const bool n_vec_ok = (p.N % OutVec<OutT>::kPerVec) == 0;
+    const bool bias_vec_ok = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;  // chunks start at multiples of 32 columns
     // 32-byte stores: every row segment starts on a 32-byte boundary (chunks start at multiples of 32 columns)
     const bool n_wide_ok = (p.N % (2 * OutVec<OutT>::kPerVec)) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 31u) == 0 && (p.debug_mode & 64) == 0;
     int acc = 0;
@@ -858,8 +859,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (p.bias != nullptr) {
           if (p.bias_axis == 0) {
+            if (valid == 32 && bias_vec_ok) {
+              // every lane needs the same 32 bias values: eight 16-byte loads instead of 32 scalar ones
+              const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) x[j] += (j < valid) ? __ldg(p.bias + col0 + j) : 0.0f;
+              for (int j = 0; j < 8; ++j) {
+                const float4 t = __ldg(b4 + j);
+                x[4 * j] += t.x;
+                x[4 * j + 1] += t.y;
+                x[4 * j + 2] += t.z;
+                x[4 * j + 3] += t.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) x[j] += (j < valid) ? __ldg(p.bias + col0 + j) : 0.0f;
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] += bias_row;
