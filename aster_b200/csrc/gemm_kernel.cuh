@@ -105,7 +105,10 @@ struct Params {
   // Bring-up aid: when non-null, every CTA writes global-timer readings (ns) of its milestones to
   // timeline[blockIdx.x * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel complete,
   // 3 first copy issued, 4 first stage landed, 5 last MMA committed, 6 last accumulator ready,
-  // 7 last epilogue done, 8 exit, 9..15 last MMA of the CTA's first seven work items committed.
+  // 7 last epilogue done, 8 exit, 9..15 last MMA of the CTA's first seven work items committed
+  // (slot 12 is then overwritten with the SM cycles of the last item's epilogue).  A stamp costs
+  // about a microsecond (the global timer is slow to read): intervals between stamps of one
+  // thread include that.
   unsigned long long* timeline;
 };
 
@@ -723,6 +726,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       tc_fence_after_sync();
       if (warp == 2 && lane == 0) stamp(p, 6);  // overwritten per item: the last one stays
+      const long long epi_c0 = clock64();
       const int row = m_blk * kTileM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -898,7 +902,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       acc = (acc + 1) % kAccBufs;
       if (acc == 0) acc_phase ^= 1u;
-      if (warp == 2 && lane == 0) stamp(p, 7);  // overwritten per item: the last one stays
+      if (warp == 2 && lane == 0) {
+        stamp(p, 7);  // overwritten per item: the last one stays
+        if (p.timeline != nullptr) p.timeline[static_cast<size_t>(blockIdx.x) * 16 + 12] = static_cast<unsigned long long>(clock64() - epi_c0);
+      }
     }
   }
 

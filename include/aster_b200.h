@@ -255,7 +255,8 @@ int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void
  * of its milestones at [cta * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel of the
  * stream complete, 3 first copy issued, 4 first stage landed, 5 last MMA committed, 6 last
  * accumulator ready, 7 last epilogue done, 8 exit, 9..15 the MMAs of the CTA's first seven work
- * items committed.  NULL detaches. */
+ * items committed (12 is then overwritten with the SM cycles of the last item's epilogue).  A
+ * stamp itself costs about a microsecond.  NULL detaches. */
 int b200_gemm_debug_timeline(b200_gemm_plan* plan, void* device_buffer);
 
 /* ---- block-scaled fp8 (dtype_ab = B200_MXE4M3 | B200_MXE5M2) -----------------------------
