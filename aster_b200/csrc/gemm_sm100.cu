@@ -270,7 +270,6 @@ struct b200_gemm_plan {
   int64_t tail_ws_bytes = 0;   // flags + partial tiles; 0 = tail split not useful for this plan
   int64_t tail_flag_bytes = 0;
   const void* tail_ws_seen = nullptr;  // workspace whose flag area has been zeroed
-  uint32_t epoch = 0;
   KernelFn kernel = nullptr;
   bool attr_set = false;
   int attr_device = -1;
@@ -472,7 +471,6 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     if (plan->tail_ws_seen != workspace) {
       B200_CUDA_OK(cudaMemsetAsync(workspace, 0, static_cast<size_t>(plan->tail_flag_bytes), stream));
       plan->tail_ws_seen = workspace;
-      plan->epoch = 0;
     }
     p.tail_tiles = plan->tail_tiles;
     p.tail_parts = plan->tail_parts;
@@ -480,8 +478,11 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     p.tail_kb = plan->tail_kb;
     p.tail_flags = static_cast<uint32_t*>(workspace);
     p.tail_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + plan->tail_flag_bytes);
-    p.epoch = ++plan->epoch;
-    if (p.epoch == 0) p.epoch = ++plan->epoch;  // 0 is the cleared state of a flag
+    // Epochs are unique across the plans of the process: a workspace that two plans take turns
+    // with never holds a flag that a later launch of the other plan could mistake for its own.
+    static std::atomic<uint32_t> next_epoch{0};
+    p.epoch = ++next_epoch;
+    if (p.epoch == 0) p.epoch = ++next_epoch;  // 0 is the cleared state of a flag
   }
   {
     // Programmatic stream serialisation: this launch may begin its prologue (barrier set-up,

@@ -164,7 +164,8 @@ typedef struct b200_gemm_resources {
    * a caller that lends a 256-byte aligned workspace of at least optional_workspace_bytes lets
    * the last tail_tiles tiles be cut into tail_parts K ranges on otherwise idle SMs (partials
    * meet in the workspace, fixed summation order).  0 = not useful for this plan.  Without the
-   * workspace the plan runs whole tiles only. */
+   * workspace the plan runs whole tiles only.  Launches that use one workspace must be ordered
+   * (one stream); plans may take turns with it. */
   int64_t optional_workspace_bytes;
   int32_t tail_tiles, tail_parts;
 } b200_gemm_resources;

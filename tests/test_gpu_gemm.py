@@ -259,6 +259,32 @@ class TestTailSplit:
         run(1024, 1024, 2048, "bf16", "bf16", "normal", 2, bias=True, relu=True, tail_split=True, tile_n=256)
         run(1024, 1024, 4096, "e4m3", "bf16", "normal", 3, tail_split=True, tile_n=256)
 
+    def test_two_plans_take_turns_with_one_workspace(self, gpu):
+        """Launch epochs are unique across plans: a flag left by one plan is never taken for the
+        other plan's (both plans below are at the same launch count when they meet)."""
+        from aster_b200 import _native as nat
+        from aster_b200.execution import GpuBuffer
+
+        shapes = [(1024, 1024, 4096), (1024, 1024, 2048)]
+        plans, inputs, bufs, outs = [], [], [], []
+        for M, N, K in shapes:
+            inp = orc.make_inputs(M, N, K, "bf16", "uniform", K)
+            plan = GemmPlan(M, N, K, "bf16", "f32", tile_n=256)
+            assert plan.resources().tail_parts >= 2
+            dA, dB, dC = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes), GpuBuffer(M * N * 4)
+            dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
+            plans.append(plan), inputs.append(inp), bufs.append((dA, dB, dC))
+        ws = GpuBuffer(max(p.resources().optional_workspace_bytes for p in plans))
+        for rnd in range(3):
+            for plan, (dA, dB, dC) in zip(plans, bufs):
+                plan.run(dA, dB, dC, workspace=ws)  # back to back, same stream, same workspace
+        nat.call("b200_device_synchronize")
+        for plan, inp, (dA, dB, dC), (M, N, K) in zip(plans, inputs, bufs, shapes):
+            plan.status()
+            out = np.empty((M, N), np.float32)
+            dC.copy_to_host(out)
+            check(out, inp, "bf16", "f32")
+
     def test_short_k_is_not_split(self, gpu):
         # the exchange costs more than a few K blocks save: such plans keep whole tiles
         assert GemmPlan(512, 512, 512, "bf16", "bf16").resources().tail_parts == 0
