@@ -620,9 +620,39 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   }
   if (bn == 0) {
     const int units = kDefaultSms / cg;  // CTAs or pairs that run at once
-    bn = 256;
-    const int narrowest = (cg == 1 && short_k && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, 32) <= units) ? 32 : 64;
-    while (bn > narrowest && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, bn) < units) bn /= 2;
+    if (cg == 1 && short_k && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, 32) <= units) {
+      bn = 32;  // the latency case above
+    } else {
+      // Estimated launch time = rounds of tiles x cost of one K block at that width.  Costs are
+      // relative to a 256-column tile and measured (fp8 probe, 8192^3: 128 columns run at 0.75 of
+      // the rate, and a 128 x 64 x 16 MMA still occupies the pipe for ~100 cycles); a last
+      // partial round counts 1/parts when the tail split can cut it, plus the exchange.
+      static const struct {
+        int bn;
+        double cost;
+      } kWidths[] = {{256, 1.0}, {128, 0.66}, {64, 0.45}};
+      double best = 0.0;
+      for (const auto& w : kWidths) {
+        const int64_t tiles = static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, w.bn);
+        const int64_t tail = tiles % units;
+        double rounds = static_cast<double>(tiles / units);
+        if (tail != 0) {
+          int parts = 1;
+          for (int cand = 8; cand >= 2; cand /= 2) {
+            if (cand <= units / tail && w.bn / cand >= 32 && k_blocks / cand >= 12) {
+              parts = cand;
+              break;
+            }
+          }
+          rounds += parts > 1 ? 1.0 / parts + 0.06 * parts : 1.0;
+        }
+        const double t = rounds * w.cost;
+        if (bn == 0 || t < best - 1e-9) {
+          bn = w.bn;
+          best = t;
+        }
+      }
+    }
     while (bn > (cg == 2 ? 64 : 32) && bn / 2 >= d.N) bn /= 2;
   }
   plan->bn = bn;
