@@ -67,6 +67,14 @@ class TestOnGpu:
         tol = 1e-6 * K * float(a.float().abs().max() * b.float().abs().max())
         assert float((c - ref).abs().max()) <= tol
 
+    def test_direct_function_equals_the_operator(self, gpu):
+        a = torch.randn(300, 520, device="cuda").bfloat16()
+        b = torch.randn(200, 520, device="cuda").bfloat16()
+        bias = torch.randn(200, device="cuda")
+        x = torch.ops.aster_b200.gemm_nt(a, b, bias, True, torch.bfloat16)
+        y = top.gemm_nt_direct(a, b, bias, True, torch.bfloat16)
+        assert torch.equal(x, y)
+
     def test_plan_cache_reuse(self, gpu):
         top.clear_plan_cache()
         a = torch.ones(128, 64, device="cuda", dtype=torch.float16)
