@@ -623,30 +623,35 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
     if (cg == 1 && short_k && static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, 32) <= units) {
       bn = 32;  // the latency case above
     } else {
-      // Estimated launch time = rounds of tiles x cost of one K block at that width.  Costs are
-      // relative to a 256-column tile and measured (fp8 probe, 8192^3: 128 columns run at 0.75 of
-      // the rate, and a 128 x 64 x 16 MMA still occupies the pipe for ~100 cycles); a last
-      // partial round counts 1/parts when the tail split can cut it, plus the exchange.
+      // Estimated launch time in microseconds, from measured constants: a K block of a
+      // 256-column tile takes 0.36 us (512 tensor-pipe cycles at the clock the power cap leaves);
+      // a 128-column tile runs at 0.75 of that rate and a 128 x 64 x 16 MMA still occupies the
+      // pipe for ~100 cycles, so narrower tiles cost 0.66 and 0.78 of a wide one per K block;
+      // HBM streams 6.2 TB/s; the partial-sum exchange of a tail split costs ~4 us and a tile's
+      // epilogue 2.6 us per 256 columns.  A last partial round counts 1/parts when the tail
+      // split can cut it.
       static const struct {
         int bn;
         double cost;
-      } kWidths[] = {{256, 1.0}, {128, 0.66}, {64, 0.45}};
+      } kWidths[] = {{256, 1.0}, {128, 0.66}, {64, 0.78}};
+      const double hbm_us = (static_cast<double>(d.M + d.N) * d.K * eb + static_cast<double>(d.M) * d.N * elt_bytes(d.dtype_c)) / 6.2e6;
       double best = 0.0;
       for (const auto& w : kWidths) {
         const int64_t tiles = static_cast<int64_t>(plan->m_blocks) * ceil_div(d.N, w.bn);
         const int64_t tail = tiles % units;
         double rounds = static_cast<double>(tiles / units);
+        int parts = 1;
         if (tail != 0) {
-          int parts = 1;
           for (int cand = 8; cand >= 2; cand /= 2) {
             if (cand <= units / tail && w.bn / cand >= 32 && k_blocks / cand >= 12) {
               parts = cand;
               break;
             }
           }
-          rounds += parts > 1 ? 1.0 / parts + 0.06 * parts : 1.0;
+          rounds += 1.0 / parts;
         }
-        const double t = rounds * w.cost;
+        const double compute_us = rounds * k_blocks * 0.36 * w.cost;
+        const double t = (compute_us > hbm_us ? compute_us : hbm_us) + (parts > 1 ? 4.0 : 0.0) + 2.6 * w.bn / 256.0;
         if (bn == 0 || t < best - 1e-9) {
           bn = w.bn;
           best = t;

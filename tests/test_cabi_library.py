@@ -99,8 +99,8 @@ def test_plan_resources_without_a_gpu(native_lib):
     p.destroy()
     p.destroy()  # idempotent
     small = GemmPlan(512, 512, 2048).resources()
-    assert small.tile_n == 64 and small.num_tiles == 16 and small.cta_group == 2
-    assert (small.tail_tiles, small.tail_parts, small.grid_ctas) == (16, 2, 64) and small.optional_workspace_bytes > 0
+    assert small.tile_n == 128 and small.num_tiles == 8 and small.cta_group == 2
+    assert (small.tail_tiles, small.tail_parts, small.grid_ctas) == (8, 2, 32) and small.optional_workspace_bytes > 0
     short = GemmPlan(512, 512, 512).resources()  # too few K blocks to pay for the exchange; small single-CTA tiles for latency
     assert (short.tail_parts, short.optional_workspace_bytes) == (0, 0)
     assert (short.cta_group, short.tile_n, short.grid_ctas) == (1, 32, 64)

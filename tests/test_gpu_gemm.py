@@ -243,7 +243,7 @@ class TestTailSplit:
     @pytest.mark.parametrize("shape,kw", [
         ((4096, 4096, 2048), {}),                                   # 256 tiles on 74 pairs: 34 tail tiles x 2 parts
         ((1024, 1024, 4096), dict(tile_n=256)),                     # 16 tiles, all tail: 4 parts
-        ((512, 512, 2048), {}),                                     # 16 small tiles x 2 parts
+        ((512, 512, 2048), {}),                                     # 8 small tiles x 2 parts
         ((1280, 512, 4096), dict(tile_n=128, max_ctas=16)),         # 20 tiles on 8 pairs: 4 tail tiles x 2 parts
         ((640, 512, 4096), dict(cta_group=1, tile_n=128, max_ctas=16)),  # single CTAs: 20 tiles on 16 CTAs -> 4 tail x 4 parts
         ((300, 200, 2056), dict(tile_n=64)),                        # ragged edges in the exchanged tiles
