@@ -132,7 +132,9 @@ typedef struct b200_gemm_desc {
   int32_t b_layout;  /* B200_B_*                                                                */
   int32_t epilogue;  /* B200_EPI_*                                                              */
   int32_t bias_axis; /* B200_BIAS_AXIS_*                                                        */
-  int32_t tile_m;    /* CTA tile rows: 128 (one CTA) or 256 (CTA pair); 0 = choose              */
+  int32_t tile_m;    /* CTA tile rows: 128 (one CTA) or 256 (CTA pair); 0 = choose.  With 0 and
+                      * M <= 64 a stage holds only 32 or 64 rows of A (more ring slots for B);
+                      * 128 asks for full A stages                                              */
   int32_t tile_n;    /* CTA tile columns: 64, 128 or 256; 0 = choose                            */
   int32_t tile_k;    /* elements per pipeline stage along K; 0 = 128 bytes' worth               */
   int32_t stages;    /* shared-memory ring depth; 0 = as many as fit                            */
