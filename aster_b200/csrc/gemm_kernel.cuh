@@ -793,6 +793,62 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + static_cast<size_t>(lo) * 8u + j * 32);
       }
+      // Whole tiles of a floating-point product (no K split of any kind, at least 64 columns) take
+      // a leaner path: 64 columns per TMEM load and wait, i.e. two independent conversion and
+      // store chains per iteration and half the loop trips.  An epilogue warp is a serial chain
+      // on one scheduler; this is the cheap way to give it instruction-level parallelism.
+      if constexpr (BN >= 64) {
+        if (!tail_item && p.split_k <= 1 && p.acc_int == 0 && (p.debug_mode & 64) == 0) {
+#pragma unroll 1
+          for (int c = 0; c < (slab_ok ? BN : 0); c += 64) {
+            uint32_t v[64];
+            tmem_ld_32x32b_x64(taddr + static_cast<uint32_t>(c), v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col0 = n_blk * BN + c + 32 * h;
+              if (col0 >= p.N) continue;  // warp-uniform
+              const int valid = min(32, p.N - col0);
+              float x[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[32 * h + j]);
+              if (alpha != 1.0f) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] *= alpha;
+              }
+              if (p.bias != nullptr) {
+                if (p.bias_axis == 0) {
+                  if (valid == 32 && bias_vec_ok) {
+                    const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                      const float4 t = __ldg(b4 + j);
+                      x[4 * j] += t.x;
+                      x[4 * j + 1] += t.y;
+                      x[4 * j + 2] += t.z;
+                      x[4 * j + 3] += t.w;
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) x[j] += (j < valid) ? __ldg(p.bias + col0 + j) : 0.0f;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) x[j] += bias_row;
+                }
+              }
+              if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
+              }
+              if (row_ok && (p.debug_mode & 32) == 0) {
+                store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
+              }
+            }
+          }
+          lo = hi;  // nothing left for the general loop below
+        }
+      }
       // One 32-column chunk of this warp's rows per iteration.  (Keeping the next chunk's TMEM
       // load in flight during the current one was tried twice: with two 32-column register sets
       // the compiler spills, which is not an option for registers that an asynchronous load is
