@@ -468,9 +468,15 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   if (plan->tail_parts > 1 && workspace != nullptr && static_cast<int64_t>(workspace_size) >= plan->tail_ws_bytes &&
       (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
     // The caller lent the optional workspace: cut the last round of tiles along K.
-    if (plan->tail_ws_seen != workspace) {
+    // A launch recorded into a CUDA graph is replayed with the epoch it was recorded with, so
+    // the flags it left would read as "written" to its own next replay: every recorded launch
+    // therefore clears the flags first (a memset node per replay), and forgets the workspace,
+    // so that the next launch outside a graph clears what the replays leave behind.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    B200_CUDA_OK(cudaStreamIsCapturing(stream, &capturing));
+    if (capturing != cudaStreamCaptureStatusNone || plan->tail_ws_seen != workspace) {
       B200_CUDA_OK(cudaMemsetAsync(workspace, 0, static_cast<size_t>(plan->tail_flag_bytes), stream));
-      plan->tail_ws_seen = workspace;
+      plan->tail_ws_seen = capturing != cudaStreamCaptureStatusNone ? nullptr : workspace;
     }
     p.tail_tiles = plan->tail_tiles;
     p.tail_parts = plan->tail_parts;
