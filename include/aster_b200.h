@@ -193,7 +193,10 @@ int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, vo
  * when the epilogue has no bias.  scale_a / scale_b: device pointers to one fp32 each
  * (per-tensor dequantisation scales), NULL = 1.0.  workspace: device scratch of at least
  * resources.workspace_bytes (may be NULL when that is 0); a workspace of at least
- * resources.optional_workspace_bytes additionally enables the tail split. */
+ * resources.optional_workspace_bytes additionally enables the tail split.
+ * `stream` may be recording a CUDA graph (create the plan beforehand: that allocates); the
+ * addresses are baked into the recorded launch, and a recorded tail-split launch carries a
+ * small memset node that clears its ready flags on every replay. */
 int b200_gemm_run(b200_gemm_plan* plan, const void* A, const void* B, void* C,
                   const float* bias, const float* scale_a, const float* scale_b,
                   void* workspace, size_t workspace_bytes, void* stream);
