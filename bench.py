@@ -649,7 +649,7 @@ def run_bandwidth(args, job: Job, w: dict, name: str) -> dict:
 # under profiles/ (null where no capture exists for the workload).
 TRAFFIC_BYTES: dict = {
     # per-launch dram__bytes_read.sum + dram__bytes_write.sum of the ncu captures summarised under profiles/
-    "bf16_4096": 136.1e6,  # 108.4 MB read + 27.7 MB written (the surplus over 100.7 MB is the tail-split exchange)
+    "bf16_4096": 133.9e6,  # 107.2 MB read + 26.7 MB written (the surplus over 100.7 MB is the tail-split exchange)
     "decode_16": 138.6e6,  # 134.55 MB read + 4.08 MB written
 }
 
