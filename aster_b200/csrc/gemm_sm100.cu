@@ -612,6 +612,12 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
         static_cast<int64_t>(ceil_div(d.M, gemm::kBM)) * ceil_div(d.N, 32) <= kDefaultSms) {  // 128 x 32 tiles still fit one round
       cg = 1;
     }
+    // A pair pays a cluster round trip per tile (accumulator hand-over, commit to both CTAs).
+    // With at most 8 K blocks per tile that outweighs the shared B traffic it saves (8192 x 8192 x
+    // 512: 66 us with single CTAs, 76 us with pairs), and so it does when all 128 x 256 tiles run
+    // in one round on more than half of the SMs (2048^3: 16.3 against 17.0 us).
+    const int64_t wide_tiles = static_cast<int64_t>(ceil_div(d.M, gemm::kBM)) * ceil_div(d.N, 256);
+    if (cg == 2 && !mx && (k_blocks <= 8 || (wide_tiles > kDefaultSms / 2 && wide_tiles <= kDefaultSms))) cg = 1;
   }
   plan->cg = cg;
   plan->mx = mx;
@@ -634,8 +640,8 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
       // a 128-column tile runs at 0.75 of that rate and a 128 x 64 x 16 MMA still occupies the
       // pipe for ~100 cycles, so narrower tiles cost 0.66 and 0.78 of a wide one per K block;
       // HBM streams 6.2 TB/s; the partial-sum exchange of a tail split costs ~4 us and a tile's
-      // epilogue 2.6 us per 256 columns.  A last partial round counts 1/parts when the tail
-      // split can cut it.
+      // epilogue 2.6 us per 256 columns; every tile adds about 0.5 us of hand-over.  A last
+      // partial round counts 1/parts when the tail split can cut it.
       static const struct {
         int bn;
         double cost;
@@ -656,7 +662,7 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
           }
           rounds += 1.0 / parts;
         }
-        const double compute_us = rounds * k_blocks * 0.36 * w.cost;
+        const double compute_us = rounds * (k_blocks * 0.36 * w.cost + 0.5);  // 0.5 us of fixed cost per tile
         const double t = (compute_us > hbm_us ? compute_us : hbm_us) + (parts > 1 ? 4.0 : 0.0) + 2.6 * w.bn / 256.0;
         if (bn == 0 || t < best - 1e-9) {
           bn = w.bn;

@@ -43,6 +43,24 @@ def _plan_for(device: torch.device, M: int, N: int, K: int, dtype_ab: str, dtype
     return hit
 
 
+_run_fn = None
+
+
+def _gemm_run():
+    global _run_fn
+    if _run_fn is None:
+        _run_fn = nat.lib().b200_gemm_run
+    return _run_fn
+
+
+def _raw_stream(device: torch.device) -> int:
+    """Handle of torch's current stream on ``device`` (0 = the default stream)."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return raw(device.index) or None
+    return torch.cuda.current_stream(device).cuda_stream or None
+
+
 _EPILOGUES = {(False, False): "none", (True, True): "bias_relu", (True, False): "bias", (False, True): "relu"}
 _ready_devices: set = set()
 
@@ -78,10 +96,13 @@ def gemm_nt_direct(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor
             nat.init_current()
             _ready_devices.add(device.index)
         plan, ws = _plan_for(device, M, N, K, _DTYPES[a.dtype], _OUT_DTYPES[out_dtype], _EPILOGUES[(bias is not None, relu)])
-        plan.run(a.data_ptr(), b.data_ptr(), out.data_ptr(), None if bias is None else bias.contiguous().data_ptr(),
-                 None if scale_a is None else scale_a.data_ptr(), None if scale_b is None else scale_b.data_ptr(),
-                 None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
-                 stream=torch.cuda.current_stream(device).cuda_stream)
+        # Straight to the entry point with plain integers (its argument types are declared, so
+        # ctypes converts them): the wrapper objects of GemmPlan.run cost more host time than a
+        # small problem's kernel runs for.
+        nat.check(_gemm_run()(
+            plan.handle, a.data_ptr(), b.data_ptr(), out.data_ptr(), None if bias is None else bias.contiguous().data_ptr(),
+            None if scale_a is None else scale_a.data_ptr(), None if scale_b is None else scale_b.data_ptr(),
+            None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(), _raw_stream(device)))
 
     if torch.cuda.current_device() == device.index:  # the C ABI works on the current device, like torch
         launch()

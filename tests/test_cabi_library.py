@@ -104,6 +104,10 @@ def test_plan_resources_without_a_gpu(native_lib):
     short = GemmPlan(512, 512, 512).resources()  # too few K blocks to pay for the exchange; small single-CTA tiles for latency
     assert (short.tail_parts, short.optional_workspace_bytes) == (0, 0)
     assert (short.cta_group, short.tile_n, short.grid_ctas) == (1, 32, 64)
+    # pairs pay per tile: at most 8 K blocks, or one round of 128 x 256 tiles on most SMs -> single CTAs
+    for shape, want in [((8192, 8192, 512), (1, 256, 148)), ((2048, 2048, 2048), (1, 256, 128)), ((4096, 4096, 1024), (2, 256, 148))]:
+        got = GemmPlan(*shape, "bf16", "bf16").resources()
+        assert (got.cta_group, got.tile_n, got.grid_ctas) == want, shape
     assert (r.tail_tiles, r.tail_parts) == (34, 2) and r.optional_workspace_bytes == 34 * (256 * 256 * 4 + 32) + 0 * 256 or r.optional_workspace_bytes > 34 * 256 * 256 * 4
     assert GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources().tail_parts == 0
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()
