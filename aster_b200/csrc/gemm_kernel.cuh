@@ -254,7 +254,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, c
     }
   }
   ok = __shfl_sync(0xffffffffu, ok, 0);
-  __threadfence();  // the other lanes' reads of the partial tile come after lane 0's acquire
+  __syncwarp();  // the other lanes' reads of the partial tile come after lane 0's acquire (the warp barrier orders memory among its lanes)
   return ok != 0;
 }
 
@@ -771,8 +771,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                          __uint_as_float(v[4 * j + 3]));
             }
           }
-          // Publish: every lane's stores are ordered before the flag the other parts poll.
-          __threadfence();
+          // Publish: the warp barrier orders every lane's stores before lane 0's release of the
+          // flag the other parts poll (a release is cumulative over what its thread has observed).
           __syncwarp();
           if (lane == 0) st_release_gpu(tile_flags + static_cast<size_t>(w.part) * (CG * 4), p.epoch);
           for (int q = 0; q < p.tail_parts; ++q) {
