@@ -615,9 +615,10 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
     // A pair pays a cluster round trip per tile (accumulator hand-over, commit to both CTAs).
     // With at most 8 K blocks per tile that outweighs the shared B traffic it saves (8192 x 8192 x
     // 512: 66 us with single CTAs, 76 us with pairs), and so it does when all 128 x 256 tiles run
-    // in one round on more than half of the SMs (2048^3: 16.3 against 17.0 us).
+    // in one round on more than half of the SMs, up to 64 K blocks (2048^3: 16.3 against 17.0 us;
+    // at 128 K blocks the pair's deeper ring and halved B traffic win: 512 x 8192 x 8192 56 against 74 us).
     const int64_t wide_tiles = static_cast<int64_t>(ceil_div(d.M, gemm::kBM)) * ceil_div(d.N, 256);
-    if (cg == 2 && !mx && (k_blocks <= 8 || (wide_tiles > kDefaultSms / 2 && wide_tiles <= kDefaultSms))) cg = 1;
+    if (cg == 2 && !mx && (k_blocks <= 8 || (k_blocks <= 64 && wide_tiles > kDefaultSms / 2 && wide_tiles <= kDefaultSms))) cg = 1;
   }
   plan->cg = cg;
   plan->mx = mx;

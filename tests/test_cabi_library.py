@@ -105,7 +105,8 @@ def test_plan_resources_without_a_gpu(native_lib):
     assert (short.tail_parts, short.optional_workspace_bytes) == (0, 0)
     assert (short.cta_group, short.tile_n, short.grid_ctas) == (1, 32, 64)
     # pairs pay per tile: at most 8 K blocks, or one round of 128 x 256 tiles on most SMs -> single CTAs
-    for shape, want in [((8192, 8192, 512), (1, 256, 148)), ((2048, 2048, 2048), (1, 256, 128)), ((4096, 4096, 1024), (2, 256, 148))]:
+    for shape, want in [((8192, 8192, 512), (1, 256, 148)), ((2048, 2048, 2048), (1, 256, 128)), ((4096, 4096, 1024), (2, 256, 148)),
+                        ((512, 8192, 8192), (2, 256, 128))]:
         got = GemmPlan(*shape, "bf16", "bf16").resources()
         assert (got.cta_group, got.tile_n, got.grid_ctas) == want, shape
     assert (r.tail_tiles, r.tail_parts) == (34, 2) and r.optional_workspace_bytes == 34 * (256 * 256 * 4 + 32) + 0 * 256 or r.optional_workspace_bytes > 34 * 256 * 256 * 4
