@@ -149,6 +149,7 @@ SIGNATURES = {
     "b200_gemm_time": [_P, _P, _P, _P, _P, _P, _P, _P, _SZ, C.c_int, C.c_int, _FP],
     "b200_gemm_time_batch": [_P, _P, _P, _P, _P, _P, _P, _P, _SZ, C.c_int, _FP],
     "b200_gemm_splitk_noalloc": [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, _P],
+    "b200_gemm_splitk_noalloc_status": [C.POINTER(C.c_uint32)],
     "b200_status_read": [_P, C.POINTER(C.c_uint32)],
     "b200_gemm_last_sm_mhz": [_P, _FP],
     "b200_launch_count": [C.POINTER(C.c_int64)],
@@ -156,7 +157,6 @@ SIGNATURES = {
     "b200_vector_add_f32": [_P, _P, _P, _SZ, _P],
     "b200_copy_2d_padded_f32": [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, _P],
     "b200_add_relu_f32": [_P, _P, _P, _SZ, _P],
-    "b200_gemm_debug_timeline": [_P, _P],
     "b200_mx_scales_bytes": [C.c_int64, C.c_int64, C.POINTER(_SZ)],
     "b200_pack_mx_scales": [_P, _P, C.c_int64, C.c_int64, _P],
     "b200_gemm_plan_set_mx_scales": [_P, _P, _P],
@@ -169,6 +169,8 @@ SIGNATURES = {
     "b200_allgather_rows_all": [_P, C.POINTER(_P), C.POINTER(_P), _SZ, C.POINTER(_P)],
 }
 _NON_STATUS = {"b200_last_error": C.c_char_p, "b200_version": C.c_char_p}
+# Present only in a bring-up build of the library (include/aster_b200_bringup.h).
+BRINGUP_SIGNATURES = {"b200_gemm_debug_timeline": [_P, _P]}
 
 _lib = None
 
@@ -192,8 +194,18 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = []
             fn.restype = restype
+        for name, argtypes in BRINGUP_SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is not None:
+                fn.argtypes = argtypes
+                fn.restype = C.c_int
         _lib = handle
     return _lib
+
+
+def is_bringup_build() -> bool:
+    """Was the loaded library built with -DB200_BRINGUP (work-skipping modes, per-CTA timeline)?"""
+    return hasattr(lib(), "b200_gemm_debug_timeline")
 
 
 def last_error() -> str:

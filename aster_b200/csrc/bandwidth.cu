@@ -186,9 +186,8 @@ int launch_elementwise(const typename Op::T* a, const typename Op::T* b, typenam
   size_t want = (n + per_cta - 1) / per_cta;
   const size_t cap = static_cast<size_t>(sm_count()) * kCtasPerSm;
   const int grid = static_cast<int>(want < cap ? (want ? want : 1) : cap);
-  static const bool narrow_only = std::getenv("ASTER_B200_COPY_16B") != nullptr;  // measurement aid
   const bool aligned32 = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 31u) == 0;
-  if (aligned32 && !narrow_only) {
+  if (aligned32) {
     elementwise_wide_kernel<Op, UNROLL / 2><<<grid, kThreads, 0, b200::as_stream(stream)>>>(a, b, c, n);
   } else if (aligned16(a) && aligned16(b) && aligned16(c)) {
     elementwise_vec_kernel<Op, UNROLL><<<grid, kThreads, 0, b200::as_stream(stream)>>>(a, b, c, n);
@@ -286,8 +285,7 @@ int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, 
   cudaStream_t s = b200::as_stream(stream);
   const float4* s4 = reinterpret_cast<const float4*>(src);
   float4* d4 = reinterpret_cast<float4*>(dst);
-  static const bool narrow_only = std::getenv("ASTER_B200_COPY_16B") != nullptr;  // measurement aid
-  if (!narrow_only && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 31u) == 0 && nvec >= 2) {
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 31u) == 0 && nvec >= 2) {
     // 32-byte walk over the even part; an odd last 16-byte vector is copied by a one-CTA launch below.
     const size_t nwide = nvec / 2;
     const Vec32* s8 = reinterpret_cast<const Vec32*>(src);

@@ -3,6 +3,7 @@
 // process-wide launch counter.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <atomic>
@@ -23,6 +24,11 @@ extern std::atomic<int64_t> g_launches;
 inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// TMA descriptor of a row-major [rows, cols] operand (element type B200_*), read in boxes of
+// box_rows x 128 bytes with the 128-byte swizzle; out-of-range parts of a box read as zero.
+// Defined in gemm_sm100.cu.
+int make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 }  // namespace b200
 

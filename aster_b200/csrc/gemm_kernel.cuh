@@ -94,14 +94,18 @@ struct Params {
   float* tail_ws;         // [tail_tiles][tail_parts][tile rows][BN] fp32, a part writes only the other parts' slices
   uint32_t* tail_flags;   // [tail_tiles][tail_parts][CG][4 epilogue warps]
   uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
-  int debug_mode;  // bits 0-1: 1 = producer signals without copying, 2 = MMA warp commits without multiplying;
-                   // bit 2: skip the tail-split exchange; bit 3: producer never signals (exercises the wait limit);
-                   // bit 4 (host only): launch without programmatic stream serialisation; bit 5: the epilogue
-                   // computes but does not store C (isolates the cost of the stores); bit 6: 16-byte stores only
+  // Bit 3 (8): fault injection for the wait-limit test -- the producer never hands a stage over,
+  // so the consumers' bounded waits must expire.  Bit 4 (16, host only): launch without
+  // programmatic stream serialisation.  The other bits exist only in bring-up builds
+  // (-DB200_BRINGUP) and make the kernel skip work, i.e. return garbage: bits 0-1: 1 = producer
+  // signals without copying, 2 = MMA warp commits without multiplying; bit 2: skip the tail-split
+  // exchange; bit 5: the epilogue computes but does not store C; bit 6: 16-byte stores only.
+  int debug_mode;
   unsigned wait_limit_ms;  // limit of every bounded wait; 0 = default
   // Non-zero: nothing that precedes a launch in its stream writes B (a weight matrix), so the
   // producer may request the first ring of B tiles before the previous kernel has completed.
   int static_b;
+#ifdef B200_BRINGUP
   // Bring-up aid: when non-null, every CTA writes global-timer readings (ns) of its milestones to
   // timeline[blockIdx.x * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel complete,
   // 3 first copy issued, 4 first stage landed, 5 last MMA committed, 6 last accumulator ready,
@@ -110,11 +114,20 @@ struct Params {
   // about a microsecond (the global timer is slow to read): intervals between stamps of one
   // thread include that.
   unsigned long long* timeline;
+#endif
 };
 
+#ifdef B200_BRINGUP
+constexpr bool kBringup = true;
 __device__ __forceinline__ void stamp(const Params& p, int slot) {
   if (p.timeline != nullptr) p.timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = sm100::globaltimer_ns();
 }
+#else
+constexpr bool kBringup = false;
+__device__ __forceinline__ void stamp(const Params&, int) {}
+#endif
+// True when a bring-up build was asked for one of the work-skipping modes in `bits`.
+__device__ __forceinline__ bool bringup_mode(const Params& p, int bits) { return kBringup && (p.debug_mode & bits) != 0; }
 
 // Block-scaled (MX) stages carry the E8M0 scales of their 128 elements of K behind the operand
 // tiles: one 512-byte block for the 128 rows of A and one per 128 rows of B, padded so that
@@ -508,7 +521,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // has completed; everything else (A, scales, all writes) comes after griddep_wait.
     int pre = 0;
     if (p.static_b != 0) {
-      if ((p.debug_mode & 11) == 0 && first_item < num_items) {
+      if ((p.debug_mode & 8) == 0 && !bringup_mode(p, 3) && first_item < num_items) {
         const WorkItem w = decode_item(p, first_item);
         int m_blk, n_blk;
         tile_coords(p, w.tile, m_blk, n_blk);
@@ -557,7 +570,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           [[maybe_unused]] const int sfb_blk = n_blk * (BN / 128);
           if (p.debug_mode & 8) {
             // injected fault: the stage is never handed over, so the consumer's wait must run out
-          } else if ((p.debug_mode & 3) == 1) {
+          } else if (kBringup && (p.debug_mode & 3) == 1) {
             if (leader) mbar_arrive(full_bar(stage));
           } else if constexpr (CG == 1) {
             if (!b_requested) arm(stage);
@@ -620,7 +633,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t full_addr = full_bar(0);
       uint32_t empty_addr = empty_bar(0);
       const uint32_t peer_delta = CG == 2 ? map_to_cta(bar_base, 1u) - bar_base : 0u;  // same offset in the peer CTA
-      const bool do_mma = (p.debug_mode & 3) != 2;
+      const bool do_mma = !(kBringup && (p.debug_mode & 3) == 2);
       const int mma_kind = p.mma_kind;
       const uint32_t idesc = p.idesc;
       [[maybe_unused]] uint32_t sf_set = 0;
@@ -710,7 +723,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const bool n_vec_ok = (p.N % OutVec<OutT>::kPerVec) == 0;
     const bool bias_vec_ok = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;  // chunks start at multiples of 32 columns
     // 32-byte stores: every row segment starts on a 32-byte boundary (chunks start at multiples of 32 columns)
-    const bool n_wide_ok = (p.N % (2 * OutVec<OutT>::kPerVec)) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 31u) == 0 && (p.debug_mode & 64) == 0;
+    const bool n_wide_ok = (p.N % (2 * OutVec<OutT>::kPerVec)) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 31u) == 0 && !bringup_mode(p, 64);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -726,7 +739,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       tc_fence_after_sync();
       if (warp == 2 && lane == 0) stamp(p, 6);  // overwritten per item: the last one stays
-      const long long epi_c0 = clock64();
+      [[maybe_unused]] long long epi_c0 = 0;
+      if constexpr (kBringup) epi_c0 = clock64();
       const int row = m_blk * kTileM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -741,7 +755,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const size_t warp_slab = static_cast<size_t>(static_cast<int>(cta_rank) * 4 + quarter) * (32u * BN);  // floats per lane quarter = 32 rows x BN
       // A warp whose 32 rows all lie beyond M has nothing to read, exchange or store.
       const bool slab_ok = (m_blk * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32) < p.M;
-      const bool exchange = (p.debug_mode & 4) == 0 && slab_ok;
+      const bool exchange = !bringup_mode(p, 4) && slab_ok;
       // Tail split: the parts of a tile (equal K ranges on different units) each finish one
       // slice of its columns.  A part first exports its partial sums for the *other* parts'
       // slices, raises its flag, waits for the others' flags and then adds their partial sums
@@ -798,7 +812,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // store chains per iteration and half the loop trips.  An epilogue warp is a serial chain
       // on one scheduler; this is the cheap way to give it instruction-level parallelism.
       if constexpr (BN >= 64) {
-        if (!tail_item && p.split_k <= 1 && p.acc_int == 0 && (p.debug_mode & 64) == 0) {
+        if (!tail_item && p.split_k <= 1 && p.acc_int == 0 && !bringup_mode(p, 64)) {
 #pragma unroll 1
           for (int c = 0; c < (slab_ok ? BN : 0); c += 64) {
             uint32_t v[64];
@@ -841,7 +855,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
               }
-              if (row_ok && (p.debug_mode & 32) == 0) {
+              if (row_ok && !bringup_mode(p, 32)) {
                 store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
               }
             }
@@ -943,7 +957,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
         }
-        if (row_ok && (p.debug_mode & 32) == 0) {
+        if (row_ok && !bringup_mode(p, 32)) {
           store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
         }
       }
@@ -960,7 +974,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (acc == 0) acc_phase ^= 1u;
       if (warp == 2 && lane == 0) {
         stamp(p, 7);  // overwritten per item: the last one stays
+#ifdef B200_BRINGUP
         if (p.timeline != nullptr) p.timeline[static_cast<size_t>(blockIdx.x) * 16 + 12] = static_cast<unsigned long long>(clock64() - epi_c0);
+#endif
       }
     }
   }
@@ -988,6 +1004,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // Split-K reduction + epilogue: C = epilogue(sum_s workspace[s]).  HBM-bound, 16-byte accesses.
 template <typename OutT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const Params p) {
+  // A main kernel whose bounded wait gave up did not write all of its partial sums: leave C alone
+  // rather than reduce whatever an earlier launch left in the workspace.
+  if (*reinterpret_cast<const volatile uint32_t*>(p.status) != kStatusOk) return;
   const float* ws = p.workspace;
   OutT* C = static_cast<OutT*>(p.C);
   float alpha = 1.0f;

@@ -15,6 +15,10 @@
 //    cleared on the stream at the start of each call, so stale contents are never consumed;
 //    but two calls that overlap on the GPU (different streams, or the same stream from two
 //    threads without ordering) race on the array and produce garbage.  Serialise them.
+//  * Every device-side wait is bounded.  If one gives up, the kernel records where in the
+//    status words, the reduction that follows sees them and leaves C untouched (it does not sum
+//    the previous call's partial sums), and b200_gemm_splitk_noalloc_status -- which allocates
+//    nothing either -- reports B200_ERR_TIMEOUT for the calls made since the last clear.
 //  * The first call on each device looks up the array's device address and sets the kernel's
 //    shared-memory attribute.  That set-up is host-side and happens once per device; make that
 //    first call before starting any stream capture.
@@ -50,34 +54,23 @@ struct DeviceSetup {
 DeviceSetup g_setup[kMaxDevices];
 std::mutex g_setup_mu;
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-int encode_operand(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess) {
-      cudaGetLastError();
-      return b200::fail(B200_ERR_CUDA, "gemm_splitk_noalloc: cuTensorMapEncodeTiled is not available from this driver");
-    }
-    fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  const uint32_t eb = dtype == B200_E4M3 ? 1u : 2u;
-  const CUtensorMapDataType dt = dtype == B200_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                 : dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                      : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * eb};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(gemm::kRowBytes / eb), box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return b200::fail(B200_ERR_CUDA, "gemm_splitk_noalloc: cuTensorMapEncodeTiled failed (%d)", (int)r);
-  return B200_OK;
+// Kernel instance for a problem: skinny problems (M <= 64) stage only 32 or 64 rows of A, as the
+// regular plan does, so that the ring holds more of B; `stages` is the ring depth that goes with it.
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const gemm::Params);
+struct Variant {
+  KernelFn fn;
+  int am;      // rows of A per stage
+  int stages;
+};
+constexpr int kMaxSmemOptin = 232448;  // 227 KB: the sm_100 per-block opt-in limit
+constexpr int stages_short_a(int am) {  // as many short-A stages as fit, up to the ring's maximum
+  const int fit = (kMaxSmemOptin - gemm::kBarrierBytes - 1024 - (gemm::kBM - am) * gemm::kRowBytes) / gemm::stage_bytes(kTileN, 1, false, am);
+  return fit < gemm::kMaxStages ? fit : gemm::kMaxStages;
+}
+Variant variant_for(int64_t M, bool f32) {
+  if (M <= 32) return {f32 ? gemm::gemm_tn_kernel<kTileN, float, 1, false, 32> : gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1, false, 32>, 32, stages_short_a(32)};
+  if (M <= 64) return {f32 ? gemm::gemm_tn_kernel<kTileN, float, 1, false, 64> : gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1, false, 64>, 64, stages_short_a(64)};
+  return {f32 ? gemm::gemm_tn_kernel<kTileN, float, 1> : gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1>, gemm::kBM, kStages};
 }
 
 int setup_device(int dev, DeviceSetup** out) {
@@ -94,11 +87,13 @@ int setup_device(int dev, DeviceSetup** out) {
     B200_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_status));
     s.status = static_cast<uint32_t*>(p);
     B200_CUDA_OK(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev));
-    const int smem = gemm::smem_bytes(kTileN, kStages, 1);
-    B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(gemm::gemm_tn_kernel<kTileN, float, 1>),
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1>),
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    for (int64_t m : {int64_t{32}, int64_t{64}, int64_t{128}}) {
+      for (bool f32 : {false, true}) {
+        const Variant v = variant_for(m, f32);
+        B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          gemm::smem_bytes(kTileN, v.stages, 1, false, v.am)));
+      }
+    }
     s.ready = true;
   }
   *out = &s;
@@ -139,9 +134,10 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
 
   CUtensorMap map_a, map_b;
   const CUtensorMap no_scales = {};  // block scales are not part of this entry point
-  rc = encode_operand(&map_a, A, dtype_ab, static_cast<uint64_t>(M), static_cast<uint64_t>(K), gemm::kBM);
+  const Variant variant = variant_for(M, dtype_c == B200_F32);
+  rc = b200::make_operand_map(&map_a, A, dtype_ab, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint32_t>(variant.am));
   if (rc != B200_OK) return rc;
-  rc = encode_operand(&map_b, B, dtype_ab, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kTileN);
+  rc = b200::make_operand_map(&map_b, B, dtype_ab, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kTileN);
   if (rc != B200_OK) return rc;
 
   gemm::Params p;
@@ -155,7 +151,7 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
   p.num_kb = (k_blocks + split - 1) / split;
   p.kb_elems = kb_elems;
   p.split_k = split;
-  p.stages = kStages;
+  p.stages = variant.stages;
   p.raster_group = 8;
   p.idesc = sm100::make_idesc(1u, dtype_ab == B200_BF16 ? 1u : 0u, dtype_ab == B200_BF16 ? 1u : 0u, gemm::kBM, kTileN);
   p.mma_kind = dtype_ab == B200_E4M3 ? sm100::kKindF8 : sm100::kKindF16;
@@ -169,12 +165,8 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
   B200_CUDA_OK(cudaMemsetAsync(setup->status, 0, 8 * sizeof(uint32_t), s));
   const int items = p.num_tiles * split;
   const int grid = items < setup->sm_count ? items : setup->sm_count;
-  const int smem = gemm::smem_bytes(kTileN, kStages, 1);
-  if (dtype_c == B200_F32) {
-    gemm::gemm_tn_kernel<kTileN, float, 1><<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, no_scales, no_scales, p);
-  } else {
-    gemm::gemm_tn_kernel<kTileN, __nv_bfloat16, 1><<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, no_scales, no_scales, p);
-  }
+  const int smem = gemm::smem_bytes(kTileN, variant.stages, 1, false, variant.am);
+  variant.fn<<<grid, gemm::kThreads, smem, s>>>(map_a, map_b, no_scales, no_scales, p);
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());
   if (split > 1) {
@@ -189,6 +181,28 @@ extern "C" int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, i
     }
     b200::count_launch();
     B200_CUDA_OK(cudaGetLastError());
+  }
+  return B200_OK;
+}
+
+// Outcome of the calls made so far on the current device, read back without allocating.
+extern "C" int b200_gemm_splitk_noalloc_status(uint32_t words[4]) {
+  B200_REQUIRE(words != nullptr, "gemm_splitk_noalloc_status: words is NULL");
+  words[0] = words[1] = words[2] = words[3] = 0;
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < kMaxDevices, "gemm_splitk_noalloc_status: device index %d not supported", dev);
+  uint32_t* status = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mu);
+    if (!g_setup[dev].ready) return B200_OK;  // never called on this device
+    status = g_setup[dev].status;
+  }
+  B200_CUDA_OK(cudaDeviceSynchronize());
+  B200_CUDA_OK(cudaMemcpy(words, status, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (words[0] != 0) {
+    return b200::fail(B200_ERR_TIMEOUT, "gemm_splitk_noalloc: device wait timed out: code 0x%x cta %u tile %u k-block %u; C of that call was not written",
+                      words[0], words[1], words[2], words[3]);
   }
   return B200_OK;
 }

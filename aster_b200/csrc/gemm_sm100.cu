@@ -8,7 +8,6 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -43,10 +42,12 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+}  // namespace
+
 // Row-major [rows, cols] matrix of `elt_bytes`-wide elements, tiled in boxes of
 // box_rows x (128 bytes of columns), written to shared memory with the 128-byte swizzle.
 // Out-of-range parts of a box read as zero, which is what makes ragged M, N and K safe.
-int make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+int b200::make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return b200::fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   CUtensorMapDataType dt;
@@ -68,6 +69,10 @@ int make_operand_map(CUtensorMap* map, const void* base, int dtype, uint64_t row
   }
   return B200_OK;
 }
+
+namespace {
+
+using b200::make_operand_map;
 
 // Packed block scales as a matrix of 32-bit words: one 512-byte row per [128 rows][4 K blocks]
 // block, copied whole and unswizzled.
@@ -252,7 +257,9 @@ struct b200_gemm_plan {
   const void* sfa = nullptr;
   const void* sfb = nullptr;
   CUtensorMap map_sfa = {}, map_sfb = {};  // all zero (never dereferenced) unless mx
-  unsigned long long* timeline = nullptr;  // bring-up aid, see b200_gemm_debug_timeline
+#ifdef B200_BRINGUP
+  unsigned long long* timeline = nullptr;  // see b200_gemm_debug_timeline
+#endif
   int stages = 0;
   int split_k = 1;
   int grid = 0;
@@ -344,7 +351,7 @@ int64_t workspace_bytes(const b200_gemm_plan* p) {
   return static_cast<int64_t>(p->split_k) * p->desc.M * p->desc.N * 4;
 }
 
-int ensure_device_state(b200_gemm_plan* plan) {
+int ensure_device_state(b200_gemm_plan* plan, cudaStream_t stream) {
   int dev = 0;
   B200_CUDA_OK(cudaGetDevice(&dev));
   if (!plan->attr_set || plan->attr_device != dev) {
@@ -391,7 +398,10 @@ int ensure_device_state(b200_gemm_plan* plan) {
     if (plan->status != nullptr) cudaFree(plan->status);
     plan->status = nullptr;
     B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&plan->status), 8 * sizeof(uint32_t)));
-    B200_CUDA_OK(cudaMemset(plan->status, 0, 8 * sizeof(uint32_t)));
+    // Cleared on the launch stream: ordered before the plan's first kernel there, whatever kind
+    // of stream it is (a memset on the legacy default stream would not be ordered against a
+    // non-blocking stream and could wipe what that first kernel reports).
+    B200_CUDA_OK(cudaMemsetAsync(plan->status, 0, 8 * sizeof(uint32_t), stream));
     plan->status_device = dev;
   }
   return B200_OK;
@@ -410,6 +420,9 @@ int check_run_args(const b200_gemm_plan* plan, const void* A, const void* B, con
     return b200::fail(B200_ERR_WORKSPACE, "gemm_run: split-K needs a %lld-byte workspace, got %zu", (long long)need,
                       workspace_bytes_in);
   }
+  // Partial sums are written and read back as 16-byte vectors.
+  B200_REQUIRE(need == 0 || (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0,
+               "gemm_run: the split-K workspace must be 16-byte aligned");
   return B200_OK;
 }
 
@@ -461,7 +474,9 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.b_packed = direct_b(plan) ? B : nullptr;
   p.workspace = static_cast<float*>(workspace);
   p.status = plan->status;
+#ifdef B200_BRINGUP
   p.timeline = plan->timeline;
+#endif
   p.static_b = (d.reserved[1] & 2) != 0 ? 1 : 0;
   p.debug_mode = d.reserved[0];
   p.wait_limit_ms = d.reserved[2] > 0 ? static_cast<unsigned>(d.reserved[2]) : 0u;
@@ -494,7 +509,6 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     // Programmatic stream serialisation: this launch may begin its prologue (barrier set-up,
     // TMEM allocation, descriptor prefetch) while the previous kernel of the stream drains; the
     // kernel waits for that kernel's completion before it touches global memory.
-    static const bool pdl_off = std::getenv("ASTER_B200_NO_PDL") != nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(plan->grid));
     cfg.blockDim = dim3(gemm::kThreads);
@@ -509,7 +523,7 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
       attr[n_attr].val.clusterDim.z = 1;
       ++n_attr;
     }
-    if (!pdl_off && (d.reserved[0] & 16) == 0) {
+    if ((d.reserved[0] & 16) == 0) {
       attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
       ++n_attr;
@@ -590,6 +604,11 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   B200_REQUIRE(d.stages >= 0 && d.stages <= gemm::kMaxStages, "gemm_plan_create: stages=%d outside [0,%d]", d.stages, gemm::kMaxStages);
   B200_REQUIRE(d.split_k >= -1 && d.split_k <= 64, "gemm_plan_create: split_k=%d outside [-1,64]", d.split_k);
   B200_REQUIRE(d.max_ctas >= 0 && d.raster_group >= 0, "gemm_plan_create: max_ctas and raster_group must be >= 0");
+#ifndef B200_BRINGUP
+  B200_REQUIRE((d.reserved[0] & ~(8 | 16)) == 0,
+               "gemm_plan_create: reserved[0]=%d asks for a work-skipping bring-up mode; those exist only in a library built with -DB200_BRINGUP",
+               d.reserved[0]);
+#endif
 
   b200_gemm_plan* plan = new (std::nothrow) b200_gemm_plan();
   if (plan == nullptr) return b200::fail(B200_ERR_INVALID, "gemm_plan_create: out of host memory");
@@ -768,12 +787,14 @@ int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, vo
   return B200_OK;
 }
 
+#ifdef B200_BRINGUP
 int b200_gemm_debug_timeline(b200_gemm_plan* plan, void* device_buffer) {
   B200_REQUIRE(plan != nullptr, "gemm_debug_timeline: plan is NULL");
   B200_REQUIRE((reinterpret_cast<uintptr_t>(device_buffer) & 7u) == 0, "gemm_debug_timeline: buffer must be 8-byte aligned");
   plan->timeline = static_cast<unsigned long long*>(device_buffer);
   return B200_OK;
 }
+#endif
 
 int b200_mx_scales_bytes(int64_t rows, int64_t K, size_t* bytes) {
   B200_REQUIRE(bytes != nullptr, "mx_scales_bytes: bytes is NULL");
@@ -816,7 +837,7 @@ int b200_gemm_run(b200_gemm_plan* plan, const void* A, const void* B, void* C, c
                   const float* scale_b, void* workspace, size_t workspace_bytes_in, void* stream) {
   int rc = check_run_args(plan, A, B, C, bias, workspace, workspace_bytes_in);
   if (rc != B200_OK) return rc;
-  rc = ensure_device_state(plan);
+  rc = ensure_device_state(plan, b200::as_stream(stream));
   if (rc != B200_OK) return rc;
   return launch(plan, A, B, C, bias, scale_a, scale_b, workspace, workspace_bytes_in, b200::as_stream(stream));
 }
@@ -827,7 +848,7 @@ int b200_gemm_time(b200_gemm_plan* plan, const void* A, const void* B, void* C, 
   B200_REQUIRE(iters >= 1 && times_ms != nullptr, "gemm_time: iters must be >= 1 and times_ms non-NULL");
   int rc = check_run_args(plan, A, B, C, bias, workspace, workspace_bytes_in);
   if (rc != B200_OK) return rc;
-  rc = ensure_device_state(plan);
+  rc = ensure_device_state(plan, nullptr);
   if (rc != B200_OK) return rc;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   B200_CUDA_OK(cudaEventCreate(&e0));
@@ -853,7 +874,7 @@ int b200_gemm_time_batch(b200_gemm_plan* plan, const void* A, const void* B, voi
   B200_REQUIRE(iters >= 1 && total_ms != nullptr, "gemm_time_batch: iters must be >= 1 and total_ms non-NULL");
   int rc = check_run_args(plan, A, B, C, bias, workspace, workspace_bytes_in);
   if (rc != B200_OK) return rc;
-  rc = ensure_device_state(plan);
+  rc = ensure_device_state(plan, nullptr);
   if (rc != B200_OK) return rc;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   B200_CUDA_OK(cudaEventCreate(&e0));

@@ -128,20 +128,6 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gsrc
                "l"(gsrc), "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t smem_src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(smem_src),
-               "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void bulk_wait_group_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void bulk_wait_group() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory and MMA
@@ -170,57 +156,9 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   }
 }
 
-// Shared-memory matrix descriptor for a K-major operand tile whose rows are 128 bytes long and
-// stored with the 128-byte swizzle (the image TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
-//   bits  0-13  start address >> 4          bits 16-29  leading byte offset >> 4 (1: unused here)
-//   bits 32-45  stride byte offset >> 4 (8 rows * 128 B = 1024 -> 64)
-//   bits 46-47  descriptor version (1 on sm_100)         bits 61-63  layout (2 = SWIZZLE_128B)
-// The tile base must be 1024-byte aligned; stepping along K inside the 128-byte row adds the
-// byte offset >> 4 to the start-address field.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
 // Operand kinds of tcgen05.mma used here: 16-bit floats (instruction K = 16), 8-bit floats and
 // 8-bit integers (K = 32: always 32 bytes of K per instruction).
 enum MmaKind : int { kKindF16 = 0, kKindF8 = 1, kKindI8 = 2 };
-
-// D[tmem] (+)= A[smem] * B[smem]^T for one instruction-K slice.  `accumulate` = 0 overwrites D.
-#define B200_MMA_ONE_ASM(GROUP, KIND)                                                           \
-  asm volatile(                                                                                 \
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"                                              \
-      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), \
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)                                     \
-      : "memory")
-
-template <int CTA_GROUP>
-__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate, int kind) {
-  if constexpr (CTA_GROUP == 1) {
-    if (kind == kKindF8) {
-      B200_MMA_ONE_ASM("1", "f8f6f4");
-    } else if (kind == kKindI8) {
-      B200_MMA_ONE_ASM("1", "i8");
-    } else {
-      B200_MMA_ONE_ASM("1", "f16");
-    }
-  } else {
-    if (kind == kKindF8) {
-      B200_MMA_ONE_ASM("2", "f8f6f4");
-    } else if (kind == kKindI8) {
-      B200_MMA_ONE_ASM("2", "i8");
-    } else {
-      B200_MMA_ONE_ASM("2", "f16");
-    }
-  }
-}
-#undef B200_MMA_ONE_ASM
 
 // The four MMAs of one pipeline stage in a single instruction sequence: D (+)= A_k . B_k^T for
 // the four 32-byte K slices of a 128-byte-swizzled stage.  `a_lo` / `b_lo` are the low words of
@@ -282,7 +220,15 @@ __device__ __forceinline__ void umma_stage(uint32_t tmem_d, uint32_t a_lo, uint3
 }
 #undef B200_MMA_STAGE_ASM
 
-// Low / high words of make_smem_desc_sw128 (the high word does not depend on the address).
+// Shared-memory matrix descriptor for a K-major operand tile whose rows are 128 bytes long and
+// stored with the 128-byte swizzle (the image TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
+//   bits  0-13  start address >> 4          bits 16-29  leading byte offset >> 4 (1: unused here)
+//   bits 32-45  stride byte offset >> 4 (8 rows * 128 B = 1024 -> 64)
+//   bits 46-47  descriptor version (1 on sm_100)         bits 61-63  layout (2 = SWIZZLE_128B)
+// The tile base must be 1024-byte aligned; stepping along K inside the 128-byte row adds the
+// byte offset >> 4 to the start-address field.
+// The descriptor is handled as its low and high 32-bit words (the high word does not depend on
+// the address).
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
 __device__ __forceinline__ constexpr uint32_t smem_desc_hi_sw128() { return (1024u >> 4) | (1u << 14) | (2u << 29); }
 
@@ -331,40 +277,15 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 __host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_format, uint32_t b_format, uint32_t umma_m, uint32_t umma_n) {
   return (a_format << 7) | (b_format << 10) | ((umma_n >> 3) << 17) | (1u << 23) | ((umma_m >> 4) << 24);
 }
-__host__ __device__ constexpr uint32_t idesc_mx_with_scale_id(uint32_t idesc, uint32_t id) { return idesc | (id << 4) | (id << 29); }
-
-// Shared-memory descriptor of a scale block: 32 rows of 16 bytes, rows contiguous (no swizzle,
-// groups of 8 rows 128 bytes apart).
-__device__ __forceinline__ uint64_t make_smem_desc_scales(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>(16 >> 4) << 16;
-  d |= static_cast<uint64_t>(128 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  return d;
-}
-
-// Copy 32 rows x 16 bytes from shared memory into four TMEM columns (row i -> lane i of each of
-// the four 32-lane quarters).  Asynchronous; ordered before later tcgen05.mma of this thread.
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-}
-
-// D[tmem] (+)= (A * scale_a) . (B * scale_b)^T for one 32-element K block, scales in TMEM.
-__device__ __forceinline__ void umma_mx_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
-                                           uint32_t tmem_scale_a, uint32_t tmem_scale_b) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_scale_a), "r"(tmem_scale_b)
-      : "memory");
-}
 
 // One block-scaled pipeline stage in a single instruction sequence: the scale blocks of the
 // stage (one for A, NB for B, 512 bytes apart in shared memory starting at the block that
 // `sf_lo` describes) go to TMEM columns sf_tmem (A) and sf_tmem + 4 .. (B), then the four MMAs
 // of the 128-byte stage follow with scale ids 0..3.  As in umma_stage, keeping the sequence in
 // one asm block keeps the issuing thread's own latency off the tensor pipe's critical path.
+// Shared-memory descriptor of a scale block (low / high word): 32 rows of 16 bytes, rows
+// contiguous (no swizzle, groups of 8 rows 128 bytes apart).  tcgen05.cp.32x128b.warpx4 copies
+// such a block into four TMEM columns (row i -> lane i of each of the four 32-lane quarters).
 __device__ __forceinline__ constexpr uint32_t smem_desc_hi_scales() { return (128u >> 4) | (1u << 14); }
 __device__ __forceinline__ uint32_t smem_desc_lo_scales(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
 

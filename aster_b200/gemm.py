@@ -211,6 +211,15 @@ def gemm_splitk_noalloc(A, B, Cbuf, M: int, N: int, K: int, dtype_ab: str = "bf1
              DTYPE_CODES[dtype_c], int(split_k), _ptr(stream))
 
 
+def gemm_splitk_noalloc_status() -> Sequence[int]:
+    """Status words of the :func:`gemm_splitk_noalloc` calls made so far on the current device
+    (synchronises it; allocates nothing).  Raises ``B200Error`` (TIMEOUT) when a bounded
+    device-side wait of the most recent call gave up -- that call left its C unwritten."""
+    words = (C.c_uint32 * 4)()
+    nat.call("b200_gemm_splitk_noalloc_status", words)
+    return list(words)
+
+
 def mx_scales_bytes(rows: int, K: int) -> int:
     """Bytes of the packed scale array for ``rows`` rows of ``K`` block-scaled elements."""
     n = C.c_size_t(0)

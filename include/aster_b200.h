@@ -143,9 +143,10 @@ typedef struct b200_gemm_desc {
   int32_t split_k;   /* K partitions reduced through an fp32 workspace; 0/1 = none, -1 = choose */
   int32_t max_ctas;  /* persistent grid size cap; 0 = number of SMs                             */
   int32_t raster_group; /* m-blocks per rasterisation group; 0 = choose                         */
-  int32_t reserved[3];  /* [0] kernel bring-up mode (0 = normal; 8 = the producer never hands a stage
-                         * over, which makes the consumer's bounded wait expire; 16 = launch without
-                         * programmatic stream serialisation), [1] bit 0 = never use the tail split,
+  int32_t reserved[3];  /* [0] 0 = normal; 8 = fault injection for tests of the wait limit: the producer
+                         * never hands a stage over, so the consumers' bounded waits expire; 16 = launch
+                         * without programmatic stream serialisation (other bits are refused unless the
+                         * library was built with -DB200_BRINGUP), [1] bit 0 = never use the tail split,
                          * bit 1 = B is static: nothing enqueued before a launch in its stream writes
                          * B (a weight matrix), so the kernel may request its first B tiles while the
                          * previous kernel of the stream is still finishing, [2] limit of the
@@ -192,7 +193,7 @@ int b200_pack_b(const b200_gemm_plan* plan, const void* b_in, void* b_packed, vo
  * plans.  C: [M,N] row-major, fully overwritten.  bias: fp32, length N (or M), may be NULL
  * when the epilogue has no bias.  scale_a / scale_b: device pointers to one fp32 each
  * (per-tensor dequantisation scales), NULL = 1.0.  workspace: device scratch of at least
- * resources.workspace_bytes (may be NULL when that is 0); a workspace of at least
+ * resources.workspace_bytes, 16-byte aligned (may be NULL when that is 0); a workspace of at least
  * resources.optional_workspace_bytes additionally enables the tail split.
  * `stream` may be recording a CUDA graph (create the plan beforehand: that allocates); the
  * addresses are baked into the recorded launch, and a recorded tail-split launch carries a
@@ -241,6 +242,13 @@ int b200_launch_count(int64_t* count);
  * Calls no cudaMalloc / cudaFree and no allocating library routine. */
 int b200_gemm_splitk_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                              int32_t dtype_ab, int32_t dtype_c, int32_t split_k, void* stream);
+/* Did the b200_gemm_splitk_noalloc calls made so far on the current device complete?  (They
+ * have no plan to pass to b200_status_read; like them, this has no counterpart in the reference
+ * and allocates nothing.)  Synchronises the device and copies back the status words of the
+ * most recent call: words[0] = 0 when every bounded device-side wait completed, else a code
+ * naming the wait that gave up, and the return value is B200_ERR_TIMEOUT; the C of such a call
+ * is left unwritten (its reduction is skipped). */
+int b200_gemm_splitk_noalloc_status(uint32_t words[4]);
 
 /* ------------------------------------------------------------------------------------------ */
 /* Bandwidth kernels                                                                          */
@@ -256,15 +264,6 @@ int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, 
                             int num_ctas, void* stream);
 /* out[i] = max(a[i] + b[i], 0); examples/07_simple_fusion/simple_fusion.py:62-144. */
 int b200_add_relu_f32(const float* a, const float* b, float* out, size_t n, void* stream);
-
-/* Bring-up aid (no counterpart in the reference): with a device buffer of grid_ctas * 16
- * uint64 words attached, every CTA of the plan's launches records global-timer readings (ns)
- * of its milestones at [cta * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel of the
- * stream complete, 3 first copy issued, 4 first stage landed, 5 last MMA committed, 6 last
- * accumulator ready, 7 last epilogue done, 8 exit, 9..15 the MMAs of the CTA's first seven work
- * items committed (12 is then overwritten with the SM cycles of the last item's epilogue).  A
- * stamp itself costs about a microsecond.  NULL detaches. */
-int b200_gemm_debug_timeline(b200_gemm_plan* plan, void* device_buffer);
 
 /* ---- block-scaled fp8 (dtype_ab = B200_MXE4M3 | B200_MXE5M2) -----------------------------
  * C = (A * 2^(sa-127)) . (B * 2^(sb-127))^T with sa[M][K/32], sb[N][K/32] bytes.  K % 32 == 0;

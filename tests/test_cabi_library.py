@@ -109,7 +109,9 @@ def test_plan_resources_without_a_gpu(native_lib):
                         ((512, 8192, 8192), (2, 256, 128))]:
         got = GemmPlan(*shape, "bf16", "bf16").resources()
         assert (got.cta_group, got.tile_n, got.grid_ctas) == want, shape
-    assert (r.tail_tiles, r.tail_parts) == (34, 2) and r.optional_workspace_bytes == 34 * (256 * 256 * 4 + 32) + 0 * 256 or r.optional_workspace_bytes > 34 * 256 * 256 * 4
+    # 34 tiles x 2 parts: fp32 partial tiles of 256 x 256 plus one ready flag per epilogue warp, padded to 256 bytes
+    assert (r.tail_tiles, r.tail_parts) == (34, 2)
+    assert r.optional_workspace_bytes == 34 * 2 * 256 * 256 * 4 + -(-(34 * 2 * 2 * 4 * 4) // 256) * 256
     assert GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources().tail_parts == 0
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()
     assert fp8.tile_k == 128
@@ -133,7 +135,33 @@ def test_run_argument_checks_do_not_need_a_gpu(native_lib):
     with pytest.raises(nat.B200Error) as e3:
         p3.run(0x1000, 0x2000, 0x3000)
     assert e3.value.status == nat.ERR_WORKSPACE
+    need = p3.resources().workspace_bytes
+    with pytest.raises(nat.B200Error, match="workspace must be 16-byte aligned") as e4:  # refused on the host: nothing is launched
+        p3.run(0x1000, 0x2000, 0x3000, workspace=0x100004, workspace_bytes=need)
+    assert e4.value.status == nat.ERR_INVALID
     assert p.status() == [0, 0, 0, 0]  # never launched
+
+
+def test_work_skipping_modes_are_not_in_the_default_build(native_lib):
+    """reserved[0] accepts the wait-limit fault injection (8) and "no dependent launch" (16); the
+    modes that make the kernel skip copies, multiplies or stores belong to the bring-up build."""
+    GemmPlan(128, 128, 128, debug_mode=8 | 16).destroy()
+    if nat.is_bringup_build():
+        pytest.skip("bring-up library loaded")
+    assert not hasattr(native_lib, "b200_gemm_debug_timeline")
+    for mode in (1, 2, 4, 32, 64):
+        with pytest.raises(nat.B200Error, match="B200_BRINGUP") as e:
+            GemmPlan(128, 128, 128, debug_mode=mode)
+        assert e.value.status == nat.ERR_INVALID
+
+
+def test_noalloc_status_reads_zero_before_any_call(native_lib):
+    words = (C.c_uint32 * 4)(7, 7, 7, 7)
+    if nat.device_count() < 1:
+        assert native_lib.b200_gemm_splitk_noalloc_status(words) != nat.OK  # no device to ask
+        assert native_lib.b200_gemm_splitk_noalloc_status(None) == nat.ERR_INVALID
+    else:
+        assert native_lib.b200_gemm_splitk_noalloc_status(None) == nat.ERR_INVALID
 
 
 def test_compile_fn_writes_an_artifact(tmp_path, native_lib):

@@ -15,7 +15,7 @@ import pytest
 
 from aster_b200 import _native as nat
 from aster_b200.execution import GpuBuffer
-from aster_b200.gemm import DTYPE_CODES, GemmPlan, gemm_splitk_noalloc
+from aster_b200.gemm import DTYPE_CODES, GemmPlan, gemm_splitk_noalloc, gemm_splitk_noalloc_status
 from oracle import gemm_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -56,7 +56,7 @@ def test_matches_regular_split_k_on_two_calls_in_a_row(gpu, M, N, K, split_k, dt
         status = nat.lib().b200_gemm_splitk_noalloc(dA.ptr, dB.ptr, dC_new.ptr, M, N, K, DTYPE_CODES[dtype_ab],
                                                      DTYPE_CODES[dtype_c], split_k, None)
         assert status == nat.OK, nat.last_error()
-        nat.call("b200_device_synchronize")
+        assert gemm_splitk_noalloc_status() == [0, 0, 0, 0]  # synchronises; no bounded wait gave up
         got = np.empty((M, N), storage)
         dC_new.copy_to_host(got)
         # Same kernels, same tile order, same summation order: the outputs are identical, which
@@ -83,7 +83,7 @@ def test_python_wrapper_and_limits(gpu):
     inp = orc.make_inputs(M, N, K, "bf16", "uniform", 4)
     dA, dB, dC, _ = _device_operands(inp, M, N, "bf16")
     gemm_splitk_noalloc(dA, dB, dC, M, N, K, "bf16", "bf16", split_k=4)
-    nat.call("b200_device_synchronize")
+    assert gemm_splitk_noalloc_status() == [0, 0, 0, 0]
     got = np.empty((M, N), np.uint16)
     dC.copy_to_host(got)
     ref = orc.gemm_f32(inp["A"], inp["B"], "bf16")
