@@ -104,6 +104,8 @@ class GemmResources(C.Structure):
         ("optional_workspace_bytes", C.c_int64),
         ("tail_tiles", C.c_int32),
         ("tail_parts", C.c_int32),
+        ("tail_exchange", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

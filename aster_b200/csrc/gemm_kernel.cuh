@@ -54,6 +54,7 @@ enum : uint32_t {
   kStatusMmaAccEmptyWait = 0x21,
   kStatusEpilogueAccFullWait = 0x30,
   kStatusTailFlagWait = 0x31,
+  kStatusClusterExchangeWait = 0x32,
 };
 
 struct Params {
@@ -94,6 +95,13 @@ struct Params {
   float* tail_ws;         // [tail_tiles][tail_parts][tile rows][BN] fp32, a part writes only the other parts' slices
   uint32_t* tail_flags;   // [tail_tiles][tail_parts][CG][4 epilogue warps]
   uint32_t epoch;         // changes every launch; a flag equal to it means "written in this launch"
+  // Non-zero: every tile is a tail tile, every CTA has exactly one part, and the `tail_parts`
+  // parts of a tile are the CTAs of one cluster (one CTA per MMA), so the partial sums are
+  // exchanged through the cluster's shared memory: each CTA parks its partial sums for the other
+  // parts' column slices in its own stage ring (idle once its last MMA has completed), signals
+  // the peers' barriers and reads its own slice out of the peers' shared memory.  No workspace,
+  // no flags in global memory.
+  int cluster_exchange;
   // Bit 3 (8): fault injection for the wait-limit test -- the producer never hands a stage over,
   // so the consumers' bounded waits must expire.  Bit 4 (16, host only): launch without
   // programmatic stream serialisation.  The other bits exist only in bring-up builds
@@ -143,7 +151,7 @@ __host__ __device__ constexpr int stage_bytes(int bn, int cg = 1, bool mx = fals
 }
 // Barrier block that follows the stage ring (and, for am < 128, the slack that the last stage's
 // 128-row A read runs into): full[16], empty[16], acc_full[2], acc_empty[2], drain, TMEM base
-// slot, abort flag.
+// slot, abort flag, and one barrier per epilogue warp for the cluster exchange.
 constexpr int kBarrierBytes = 384;
 __host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1, bool mx = false, int am = kBM) {
   return stages * stage_bytes(bn, cg, mx, am) + (kBM - am) * kRowBytes + kBarrierBytes + 1024;
@@ -186,14 +194,17 @@ struct Waiter {
   // main loop of slack): lane 0 polls with a sleep between polls, the other lanes idle at the
   // shuffle.  128 threads spinning on a barrier for the length of a main loop burn power that
   // the tensor pipe could use -- the kernel runs against the board's power limit.
+  // kClusterScope: the arrivals come from other CTAs of the cluster (acquire at cluster scope).
+  template <bool kClusterScope = false>
   __device__ __forceinline__ bool wait_relaxed(uint32_t bar, uint32_t parity, uint32_t code, int tile, unsigned sleep_ns) const {
+    auto poll = [&]() { return kClusterScope ? sm100::mbar_try_wait_cluster(bar, parity) : sm100::mbar_try_wait(bar, parity); };
     int ok = 1;
-    if ((threadIdx.x & 31) == 0 && !sm100::mbar_try_wait(bar, parity)) {
+    if ((threadIdx.x & 31) == 0 && !poll()) {
       unsigned long long t0 = sm100::globaltimer_ns();
 #pragma unroll 1
       for (uint32_t spin = 1;; ++spin) {
         __nanosleep(sleep_ns);
-        if (sm100::mbar_try_wait(bar, parity)) break;
+        if (poll()) break;
         if ((spin & 15u) == 0u) {
           if (*abort_flag != 0u) {
             ok = 0;
@@ -212,7 +223,9 @@ struct Waiter {
         }
       }
     }
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();  // the other lanes' reads come after lane 0's acquire (the warp barrier orders memory among its lanes)
+    return ok != 0;
   }
 
   __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, uint32_t code, int tile, int kb,
@@ -435,6 +448,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto empty_bar = [&](int s) { return bar_base + 128u + 8u * s; };
   auto acc_full_bar = [&](int a) { return bar_base + 256u + 8u * a; };
   auto acc_empty_bar = [&](int a) { return bar_base + 272u + 8u * a; };
+  auto xchg_bar = [&](int q) { return bar_base + 320u + 8u * q; };
   const uint32_t drain_bar = bar_base + 288u;
   const uint32_t tmem_slot = bar_base + 296u;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bar_ptr + 296);
@@ -456,6 +470,54 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int first_item = static_cast<int>(blockIdx.x) / CG;    // one work item per CTA (pair) at a time
   const int item_stride = static_cast<int>(gridDim.x) / CG;
 
+  // B tile of ring slot `stg` for K block `kb_abs` (called by the producer's elected lane).
+  auto issue_b = [&](int stg, int n_blk_, int b_row_, int kb_abs) {
+    const uint32_t b_dst = smem_base + stg * kStageBytes + kABytes;
+    const int k_elem = kb_abs * p.kb_elems;
+    if constexpr (CG == 1) {
+      if (p.b_packed != nullptr) {
+        const size_t blk = static_cast<size_t>(n_blk_) * (static_cast<size_t>(p.num_kb) * p.split_k) + kb_abs;
+        bulk_load_1d(b_dst, static_cast<const uint8_t*>(p.b_packed) + blk * kBBytes, kBBytes, full_bar(stg));
+      } else {
+        tma_load_2d(b_dst, &tmap_b, full_bar(stg), k_elem, b_row_);
+      }
+    } else {
+      tma_load_2d_pair(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_);
+    }
+  };
+  // Arm the slot's barrier with the bytes of all copies of the stage (both CTAs' in a pair,
+  // where every copy completes on the leader's barrier).
+  auto arm = [&](int stg) {
+    if constexpr (CG == 1) {
+      mbar_arrive_expect_tx(full_bar(stg), kLoadBytes);
+    } else {
+      if (leader) mbar_arrive_expect_tx(full_bar(stg), 2u * kLoadBytes);
+    }
+  };
+  // Static B (a weight matrix that nothing earlier in the stream writes): the producer warp
+  // requests the first ring of B tiles before the previous kernel of the stream has completed;
+  // everything else (A, scales, all writes) comes after griddep_wait.  Returns the slots armed.
+  auto request_first_ring = [&]() -> int {
+    int n = 0;
+    if ((p.debug_mode & 8) == 0 && !bringup_mode(p, 3) && first_item < num_items) {
+      const WorkItem w = decode_item(p, first_item);
+      int m_blk, n_blk;
+      tile_coords(p, w.tile, m_blk, n_blk);
+      const int b_row = n_blk * BN + static_cast<int>(cta_rank * kBRows);
+      n = min(p.stages, w.nkb);
+      if (elect_one()) {
+        stamp(p, 3);
+        for (int kb = 0; kb < n; ++kb) {
+          arm(kb);
+          issue_b(kb, n_blk, b_row, w.kb0 + kb);
+        }
+      }
+      __syncwarp();
+    }
+    return n;
+  };
+  int pre = 0;  // ring slots whose B tile is already on its way when the producer loop starts
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -466,6 +528,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(acc_empty_bar(a), kEpilogueWarps * CG);
     }
     mbar_init(drain_bar, 1);
+    if constexpr (CG == 1) {
+      if (p.cluster_exchange != 0) {
+        for (int q = 0; q < kEpilogueWarps; ++q) mbar_init(xchg_bar(q), static_cast<uint32_t>(p.tail_parts - 1));  // the same warp of every other part
+      }
+    }
     *abort_flag = 0u;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -476,10 +543,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       prefetch_tensormap(&tmap_sfb);
     }
   }
+  if constexpr (CG == 1) {
+    // One CTA per tile: the full[] barriers are this CTA's own, so the request can go out right
+    // behind their initialisation (same warp), ahead of the TMEM allocation and the barriers below.
+    if (warp == 0 && p.static_b != 0) {
+      __syncwarp();
+      pre = request_first_ring();
+    }
+  }
   if (warp == 1) tmem_alloc<CG>(tmem_slot, kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
-  if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
+  // the peers' barriers exist before anyone signals them
+  if constexpr (CG == 2) {
+    cluster_sync_all();
+  } else {
+    if (p.cluster_exchange != 0) cluster_sync_all();
+  }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
   // Everything above touched only this CTA's shared and tensor memory.  From here on global
@@ -487,56 +567,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // one may already set itself up behind this one (it waits at this same point).
   if (threadIdx.x == 0) stamp(p, 1);
   griddep_launch_dependents();
-  if (warp != 0 || p.static_b == 0) griddep_wait();  // the producer of a static-B plan waits after its early B requests
+  if (CG == 1 || warp != 0 || p.static_b == 0) griddep_wait();  // the producer of a static-B pair plan waits after its early B requests
   if (threadIdx.x == 32) stamp(p, 2);
 
   if (warp == 0) {
     // ------------------------------- producer -------------------------------
     // The whole warp walks the loop (every lane polls the barrier); one elected lane issues.
-    // B tile of ring slot `stg` for K block `kb_abs` (called by the elected lane).
-    auto issue_b = [&](int stg, int n_blk_, int b_row_, int kb_abs) {
-      const uint32_t b_dst = smem_base + stg * kStageBytes + kABytes;
-      const int k_elem = kb_abs * p.kb_elems;
-      if constexpr (CG == 1) {
-        if (p.b_packed != nullptr) {
-          const size_t blk = static_cast<size_t>(n_blk_) * (static_cast<size_t>(p.num_kb) * p.split_k) + kb_abs;
-          bulk_load_1d(b_dst, static_cast<const uint8_t*>(p.b_packed) + blk * kBBytes, kBBytes, full_bar(stg));
-        } else {
-          tma_load_2d(b_dst, &tmap_b, full_bar(stg), k_elem, b_row_);
-        }
-      } else {
-        tma_load_2d_pair(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_);
+    if constexpr (CG == 2) {
+      if (p.static_b != 0) {
+        pre = request_first_ring();  // the follower's copies complete on the leader's barriers: only after the cluster barrier
+        griddep_wait();
       }
-    };
-    // Arm the slot's barrier with the bytes of all copies of the stage (both CTAs' in a pair,
-    // where every copy completes on the leader's barrier).
-    auto arm = [&](int stg) {
-      if constexpr (CG == 1) {
-        mbar_arrive_expect_tx(full_bar(stg), kLoadBytes);
-      } else {
-        if (leader) mbar_arrive_expect_tx(full_bar(stg), 2u * kLoadBytes);
-      }
-    };
-    // Static B: the first ring of B tiles is requested before the previous kernel of the stream
-    // has completed; everything else (A, scales, all writes) comes after griddep_wait.
-    int pre = 0;
-    if (p.static_b != 0) {
-      if ((p.debug_mode & 8) == 0 && !bringup_mode(p, 3) && first_item < num_items) {
-        const WorkItem w = decode_item(p, first_item);
-        int m_blk, n_blk;
-        tile_coords(p, w.tile, m_blk, n_blk);
-        const int b_row = n_blk * BN + static_cast<int>(cta_rank * kBRows);
-        pre = min(p.stages, w.nkb);
-        if (elect_one()) {
-          stamp(p, 3);
-          for (int kb = 0; kb < pre; ++kb) {
-            arm(kb);
-            issue_b(kb, n_blk, b_row, w.kb0 + kb);
-          }
-        }
-        __syncwarp();
-      }
-      griddep_wait();
     }
     int stage = 0;
     uint32_t phase = 0;
@@ -733,7 +774,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int split = w.split;
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
-      if (!waiter.wait_relaxed(acc_full_bar(acc), acc_phase, kStatusEpilogueAccFullWait, tile, 256u)) {
+      // A CTA with a single work item has no later main loop for this wait to hide behind: poll
+      // tightly there (the launch ends with this epilogue); otherwise sleep between polls.
+      if (!waiter.wait_relaxed(acc_full_bar(acc), acc_phase, kStatusEpilogueAccFullWait, tile, num_items <= item_stride ? 20u : 256u)) {
         ok = false;
         break;
       }
@@ -766,11 +809,49 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const size_t part_stride4 = tail_tile_elems / 4;   // float4 per partial tile
       float4* const tile_regions = reinterpret_cast<float4*>(p.tail_ws + static_cast<size_t>(w.tail_index) * p.tail_parts * tail_tile_elems + warp_slab) + lane;
       uint32_t* const tile_flags = p.tail_flags + static_cast<size_t>(w.tail_index) * p.tail_parts * (CG * 4) + flag_lane;
+      // Cluster exchange: this lane's float4 column of this warp's slab in the CTA's own parking
+      // area, the start of the (by now idle) stage ring; same "register image" order.
+      bool via_cluster = false;
+      if constexpr (CG == 1) via_cluster = p.cluster_exchange != 0;
+      const uint32_t park = smem_base + static_cast<uint32_t>(quarter) * (32u * BN * 4u) + static_cast<uint32_t>(lane) * 16u;
+      // float4 j of chunk c of part q's partial sums for this lane.
+      auto partial = [&](int q, int c, int j) -> float4 {
+        if (via_cluster) return ld_shared_cluster_f4(map_to_cta(park, static_cast<uint32_t>(q)) + static_cast<uint32_t>(c * 8 + j * 32) * 16u);
+        return __ldcg(tile_regions + static_cast<size_t>(q) * part_stride4 + static_cast<size_t>(c) * 8u + j * 32);
+      };
       if (tail_item) {
         const int slice = BN / p.tail_parts;  // a multiple of 32 (the plan sees to it)
         lo = w.part * slice;
         hi = slab_ok ? lo + slice : lo;
-        if (exchange) {
+        if (exchange && via_cluster) {
+          // The accumulator is complete, so every stage of the ring has been consumed and nothing
+          // more is on its way into it (one work item per CTA): park the other parts' slices there.
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            if ((c >= lo && c < lo + slice) || n_blk * BN + c >= p.N) continue;  // own slice, or beyond the matrix
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(c), v);
+            tmem_ld_wait();
+            const uint32_t dst = park + static_cast<uint32_t>(c) * 128u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              st_shared_f4(dst + j * 512u, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                           __uint_as_float(v[4 * j + 3]));
+            }
+          }
+          // Publish to the same warp of every other part (release at cluster scope, cumulative over
+          // what the warp barrier made lane 0 observe), then wait for theirs.
+          __syncwarp();
+          if (lane == 0) {
+            for (int q = 0; q < p.tail_parts; ++q) {
+              if (q != w.part) mbar_arrive_remote(map_to_cta(xchg_bar(quarter), static_cast<uint32_t>(q)));
+            }
+          }
+          if (!waiter.template wait_relaxed<true>(xchg_bar(quarter), 0u, kStatusClusterExchangeWait, tile, 32u)) {
+            ok = false;
+            break;
+          }
+        } else if (exchange) {
           float4* const mine = tile_regions + static_cast<size_t>(w.part) * part_stride4;
 #pragma unroll 1
           for (int c = 0; c < BN; c += 32) {
@@ -801,11 +882,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       // This lane's float4 column of the first other part's partial tile; its first chunk is loaded now.
       const int first_other = w.part == 0 ? 1 : 0;
-      const float4* tail_src = tile_regions + static_cast<size_t>(first_other) * part_stride4;
       float4 ahead[8];
       if (tail_item && exchange && lo < hi) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(tail_src + static_cast<size_t>(lo) * 8u + j * 32);
+        for (int j = 0; j < 8; ++j) ahead[j] = partial(first_other, lo, j);
       }
       // Whole tiles of a floating-point product (no K split of any kind, at least 64 columns) take
       // a leaner path: 64 columns per TMEM load and wait, i.e. two independent conversion and
@@ -910,16 +990,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             x[4 * j + 3] += ahead[j].w;
           }
           if (c + 32 < hi) {
-            const float4* nxt = tail_src + static_cast<size_t>(c + 32) * 8u;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(nxt + j * 32);
+            for (int j = 0; j < 8; ++j) ahead[j] = partial(first_other, c + 32, j);
           }
           for (int q = first_other + 1; q < p.tail_parts; ++q) {
             if (q == w.part) continue;
-            const float4* src = tile_regions + static_cast<size_t>(q) * part_stride4 + static_cast<size_t>(c) * 8u;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 t = __ldcg(src + j * 32);
+              const float4 t = partial(q, c, j);
               x[4 * j] += t.x;
               x[4 * j + 1] += t.y;
               x[4 * j + 2] += t.z;
@@ -984,7 +1062,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // ------------------------------- teardown -------------------------------
   tc_fence_before_sync();
   __syncthreads();
-  if constexpr (CG == 2) cluster_sync_all();  // neither CTA leaves while the other may still signal it
+  // no CTA leaves while another of its cluster may still signal it or read its shared memory
+  if constexpr (CG == 2) {
+    cluster_sync_all();
+  } else {
+    if (p.cluster_exchange != 0) cluster_sync_all();
+  }
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, kTmemCols);

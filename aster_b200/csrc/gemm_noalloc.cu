@@ -90,8 +90,9 @@ int setup_device(int dev, DeviceSetup** out) {
     for (int64_t m : {int64_t{32}, int64_t{64}, int64_t{128}}) {
       for (bool f32 : {false, true}) {
         const Variant v = variant_for(m, f32);
-        B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          gemm::smem_bytes(kTileN, v.stages, 1, false, v.am)));
+        // The per-block limit rather than this variant's footprint: the instance is shared with the
+        // plans of b200_gemm_run, which set the same ceiling.
+        B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn), cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemOptin));
       }
     }
     s.ready = true;

@@ -276,6 +276,10 @@ struct b200_gemm_plan {
   int tail_tiles = 0, tail_parts = 0, tail_kb0 = 0, tail_kb = 0;
   int64_t tail_ws_bytes = 0;   // flags + partial tiles; 0 = tail split not useful for this plan
   int64_t tail_flag_bytes = 0;
+  // The parts of every tile are the CTAs of one cluster and exchange their partial sums through
+  // its shared memory (see gemm::Params::cluster_exchange); needs no workspace.
+  bool cluster_exchange = false;
+  bool cluster_exchange_ok = true;  // cleared when the device cannot co-schedule the clusters
   const void* tail_ws_seen = nullptr;  // workspace whose flag area has been zeroed
   KernelFn kernel = nullptr;
   bool attr_set = false;
@@ -303,6 +307,7 @@ int64_t packed_b_bytes(const b200_gemm_plan* p) {
 void plan_tail_split(b200_gemm_plan* plan) {
   plan->tail_tiles = plan->tail_parts = plan->tail_kb0 = plan->tail_kb = 0;
   plan->tail_ws_bytes = plan->tail_flag_bytes = 0;
+  plan->cluster_exchange = false;
   if (plan->split_k > 1 || (plan->desc.reserved[1] & 1) != 0) return;  // reserved[1] bit 0: caller opted out
   if (plan->desc.dtype_ab == B200_I8) return;  // partial tiles are exchanged as fp32; s32 sums stay whole
   const int units = plan->units_cap;
@@ -330,6 +335,15 @@ void plan_tail_split(b200_gemm_plan* plan) {
   plan->tail_parts = parts;
   plan->tail_kb0 = tail_kb;
   plan->tail_kb = tail_kb;
+  // One round, one part per CTA (skinny problems: a few column tiles, a long K): the parts of a
+  // tile form a cluster and exchange through its shared memory.  The parking area (a 128 x BN
+  // fp32 tile) must fit in the stage ring.  reserved[1] bit 2 keeps the exchange in the workspace.
+  if (plan->cg == 1 && !plan->mx && plan->cluster_exchange_ok && (plan->desc.reserved[1] & 4) == 0 && tail == tiles &&
+      tiles * parts <= units &&
+      static_cast<int64_t>(plan->stages) * gemm::stage_bytes(plan->bn, 1, false, plan->am) >= static_cast<int64_t>(gemm::kBM) * plan->bn * 4) {
+    plan->cluster_exchange = true;
+    return;  // no flags, no partial tiles in global memory
+  }
   const int64_t flags = static_cast<int64_t>(tail) * parts * plan->cg * gemm::kEpilogueWarps * sizeof(uint32_t);
   plan->tail_flag_bytes = (flags + 255) / 256 * 256;
   plan->tail_ws_bytes = plan->tail_flag_bytes + static_cast<int64_t>(tail) * parts * (gemm::kBM * plan->cg) * plan->bn * sizeof(float);
@@ -360,8 +374,11 @@ int ensure_device_state(b200_gemm_plan* plan, cudaStream_t stream) {
     if (cc_major != 10) {
       return b200::fail(B200_ERR_NO_DEVICE, "device %d has compute capability %d.x; the GEMM kernels need sm_100", dev, cc_major);
     }
+    // The limit, not this plan's own footprint: kernel instances are shared by all plans (and by
+    // b200_gemm_splitk_noalloc), and a later plan with a shallower ring must not lower the
+    // ceiling under an earlier one with a deeper ring.
     B200_CUDA_OK(cudaFuncSetAttribute(reinterpret_cast<const void*>(plan->kernel),
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, plan->smem));
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemOptin));
     int sms = kDefaultSms;
     B200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     plan->sm_count = sms;
@@ -389,6 +406,27 @@ int ensure_device_state(b200_gemm_plan* plan, cudaStream_t stream) {
       if (units_cap > clusters) units_cap = clusters;
     }
     size_grid(plan, units_cap);
+    if (plan->cluster_exchange) {
+      // All clusters of the launch must be resident at once (each CTA waits for its peers).
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(plan->grid));
+      cfg.blockDim = dim3(gemm::kThreads);
+      cfg.dynamicSmemBytes = static_cast<size_t>(plan->smem);
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(plan->tail_parts);
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, reinterpret_cast<const void*>(plan->kernel), &cfg) != cudaSuccess ||
+          clusters * plan->tail_parts < plan->grid) {
+        cudaGetLastError();
+        plan->cluster_exchange_ok = false;  // exchange through the workspace instead, when the caller lends one
+        size_grid(plan, units_cap);
+      }
+    }
     plan->tail_ws_seen = nullptr;
     plan->attr_set = true;
     plan->attr_device = dev;
@@ -480,8 +518,14 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.static_b = (d.reserved[1] & 2) != 0 ? 1 : 0;
   p.debug_mode = d.reserved[0];
   p.wait_limit_ms = d.reserved[2] > 0 ? static_cast<unsigned>(d.reserved[2]) : 0u;
-  if (plan->tail_parts > 1 && workspace != nullptr && static_cast<int64_t>(workspace_size) >= plan->tail_ws_bytes &&
-      (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
+  if (plan->tail_parts > 1 && plan->cluster_exchange) {
+    p.tail_tiles = plan->tail_tiles;
+    p.tail_parts = plan->tail_parts;
+    p.tail_kb0 = plan->tail_kb0;
+    p.tail_kb = plan->tail_kb;
+    p.cluster_exchange = 1;
+  } else if (plan->tail_parts > 1 && workspace != nullptr && static_cast<int64_t>(workspace_size) >= plan->tail_ws_bytes &&
+             (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
     // The caller lent the optional workspace: cut the last round of tiles along K.
     // A launch recorded into a CUDA graph is replayed with the epoch it was recorded with, so
     // the flags it left would read as "written" to its own next replay: every recorded launch
@@ -516,9 +560,9 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     unsigned n_attr = 0;
-    if (plan->cg == 2) {
+    if (plan->cg == 2 || p.cluster_exchange != 0) {
       attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-      attr[n_attr].val.clusterDim.x = 2;
+      attr[n_attr].val.clusterDim.x = plan->cg == 2 ? 2u : static_cast<unsigned>(plan->tail_parts);
       attr[n_attr].val.clusterDim.y = 1;
       attr[n_attr].val.clusterDim.z = 1;
       ++n_attr;
@@ -762,6 +806,7 @@ int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* ou
   out->optional_workspace_bytes = plan->tail_ws_bytes;
   out->tail_tiles = plan->tail_tiles;
   out->tail_parts = plan->tail_parts;
+  out->tail_exchange = plan->tail_parts > 1 ? (plan->cluster_exchange ? 2 : 1) : 0;
   // Registers per thread come from the loaded function; without a device this stays -1.
   out->regs_per_thread = -1;
   cudaFuncAttributes fa;

@@ -42,6 +42,8 @@ class GemmPlan:
     library choose (``split_k=-1``: choose a K split for skinny problems).  ``static_b=True``
     declares that nothing enqueued before a launch in its stream writes B (a weight matrix):
     the kernel may then request its first B tiles while the previous kernel is still finishing.
+    ``workspace_exchange=True`` makes a tail split meet in the lent workspace even where the
+    parts of a tile could form a cluster and meet in its shared memory (same sums, same order).
     """
 
     def __init__(
@@ -68,6 +70,7 @@ class GemmPlan:
         no_tail_split: bool = False,
         wait_limit_ms: int = 0,
         static_b: bool = False,
+        workspace_exchange: bool = False,
     ) -> None:
         self._handle = None
         desc = nat.GemmDesc()
@@ -83,8 +86,8 @@ class GemmPlan:
         desc.tile_m, desc.tile_n, desc.tile_k = tile_m, tile_n, tile_k
         desc.stages, desc.cta_group, desc.split_k = stages, cta_group, split_k
         desc.max_ctas, desc.raster_group = max_ctas, raster_group
-        desc.reserved[0] = debug_mode  # kernel bring-up aid: 1 = no copies, 2 = no multiplies (results are garbage)
-        desc.reserved[1] = (1 if no_tail_split else 0) | (2 if static_b else 0)
+        desc.reserved[0] = debug_mode  # 8 = wait-limit fault injection, 16 = no dependent launch (others: bring-up builds only)
+        desc.reserved[1] = (1 if no_tail_split else 0) | (2 if static_b else 0) | (4 if workspace_exchange else 0)
         desc.reserved[2] = wait_limit_ms
         desc.label = label.encode()[:255]
         handle = C.c_void_p()

@@ -149,7 +149,8 @@ typedef struct b200_gemm_desc {
                          * library was built with -DB200_BRINGUP), [1] bit 0 = never use the tail split,
                          * bit 1 = B is static: nothing enqueued before a launch in its stream writes
                          * B (a weight matrix), so the kernel may request its first B tiles while the
-                         * previous kernel of the stream is still finishing, [2] limit of the
+                         * previous kernel of the stream is still finishing, bit 2 = a tail split
+                         * exchanges through the workspace even where a cluster could, [2] limit of the
                          * device-side waits in ms (0 = 2000) */
   char label[256];   /* provenance only: the reference label string (gemm_config.py:678-701)    */
 } b200_gemm_desc;
@@ -172,6 +173,12 @@ typedef struct b200_gemm_resources {
    * (one stream); plans may take turns with it. */
   int64_t optional_workspace_bytes;
   int32_t tail_tiles, tail_parts;
+  /* How the parts of a cut tile meet: 0 = no tail split, 1 = through the lent workspace,
+   * 2 = through the shared memory of a thread-block cluster (skinny problems whose tiles all fit
+   * in one round: the parts of a tile are the CTAs of one cluster; needs no workspace and is
+   * always on; reserved[1] bit 2 of the description asks for the workspace form instead). */
+  int32_t tail_exchange;
+  int32_t reserved0;
 } b200_gemm_resources;
 
 typedef struct b200_gemm_plan b200_gemm_plan;

@@ -40,9 +40,9 @@ def test_binding_covers_every_declared_symbol():
 
 
 def test_struct_sizes_match_header_layout(native_lib):
-    # int64 x3 + int32 x16 + char[256]; int32 x12 + int64 x3; char[128] + int32 x10 + int64
+    # int64 x3 + int32 x16 + char[256]; int32 x12 + int64 x4 + int32 x4; char[128] + int32 x10 + int64
     assert C.sizeof(nat.GemmDesc) == 24 + 64 + 256
-    assert C.sizeof(nat.GemmResources) == 48 + 24 + 16
+    assert C.sizeof(nat.GemmResources) == 48 + 32 + 16
     assert C.sizeof(nat.Props) == 128 + 40 + 8
 
 

@@ -589,6 +589,23 @@ class TestDependentLaunch:
         assert np.array_equal(plain, no_pdl)
 
 
+class TestSharedKernelInstances:
+    def test_plans_with_different_rings_take_turns(self, gpu):
+        """Plans of one tile shape share a kernel instance whatever their ring depth: a plan with a
+        shallow ring set up after a deep one must not leave the deep one unable to launch."""
+        M, N, K = 256, 256, 2048
+        inp = orc.make_inputs(M, N, K, "bf16", "uniform", 11)
+        kw = dict(dtype_ab="bf16", dtype_c="f32")
+        deep = GemmPlan(M, N, K, "bf16", "f32", tile_n=128, cta_group=1, stages=6)
+        shallow = GemmPlan(M, N, K, "bf16", "f32", tile_n=128, cta_group=1, stages=2)
+        assert deep.resources().smem_bytes > shallow.resources().smem_bytes
+        first = gemm(inp["A"], inp["B"], plan=deep, **kw)
+        second = gemm(inp["A"], inp["B"], plan=shallow, **kw)
+        third = gemm(inp["A"], inp["B"], plan=deep, **kw)
+        assert np.array_equal(first, second) and np.array_equal(first, third)
+        check(first, inp, "bf16", "f32")
+
+
 class TestSkinnyM:
     """M <= 64: stages hold only 32 or 64 rows of A (more ring slots for B).  Same MMAs in the
     same order as with full A stages, so the results are bit-identical to ``tile_m=128``."""
@@ -603,6 +620,58 @@ class TestSkinnyM:
         full = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", tile_m=128, **kw)
         assert np.array_equal(short, full)
         check(short, inp, "bf16", "bf16")
+
+    @pytest.mark.parametrize("M,N,K,kw,parts", [
+        (16, 1024, 4096, dict(tile_n=64), 2),                   # 16 tiles x 2 parts: clusters of two
+        (16, 1024, 4096, dict(tile_n=128), 4),                  # 8 tiles x 4 parts: clusters of four
+        (128, 8192, 4096, dict(tile_n=128), 2),                 # full A stages, all four epilogue warps exchange
+        (100, 1000, 8192, dict(tile_n=128), 4),                 # ragged rows and columns in the exchanged tiles
+        (64, 512, 8192, dict(tile_n=256), 8),                   # 2 tiles x 8 parts: clusters of eight
+        (16, 8192, 4096, dict(tile_n=128, b_layout="packed", static_b=True), 2),  # direct-B, as the decode workloads run
+    ])
+    @pytest.mark.parametrize("dtype_c", ["bf16", "f32"])
+    def test_cluster_exchange_equals_workspace_exchange_bitwise(self, gpu, M, N, K, kw, parts, dtype_c):
+        """One round of tiles, each cut along K: the parts of a tile are the CTAs of a cluster and
+        meet in its shared memory.  Same partial sums added in the same order as when they meet
+        in the lent workspace, so the two forms agree bit for bit, and with the oracle."""
+        res = GemmPlan(M, N, K, "bf16", dtype_c, **kw).resources()
+        assert (res.tail_parts, res.tail_exchange, res.optional_workspace_bytes) == (parts, 2, 0)
+        assert res.grid_ctas == res.num_tiles * parts
+        via_ws = GemmPlan(M, N, K, "bf16", dtype_c, workspace_exchange=True, **kw).resources()
+        assert (via_ws.tail_parts, via_ws.tail_exchange) == (parts, 1) and via_ws.optional_workspace_bytes > 0
+        inp = orc.make_inputs(M, N, K, "bf16", "uniform", 4, with_bias=True)
+        common = dict(dtype_ab="bf16", dtype_c=dtype_c, bias=inp["bias"], relu=True)
+        cluster = gemm(inp["A"], inp["B"], **common, **kw)
+        workspace = gemm(inp["A"], inp["B"], **common, tail_split=True, workspace_exchange=True, **kw)
+        assert np.array_equal(cluster, workspace)
+        check(cluster, inp, "bf16", dtype_c, bias=inp["bias"], relu=True)
+
+    def test_cluster_exchange_back_to_back_launches(self, gpu):
+        """The parking area is the stage ring: a launch must not disturb the next one (dependent
+        launches overlap the next launch's prologue with this one's end)."""
+        from aster_b200 import _native as nat
+        from aster_b200.execution import GpuBuffer
+
+        M, N, K = 16, 4096, 4096
+        inp = orc.make_inputs(M, N, K, "bf16", "uniform", 9)
+        plan = GemmPlan(M, N, K, "bf16", "bf16", tile_n=128)
+        assert plan.resources().tail_exchange == 2
+        dA, dB = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes)
+        dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
+        outs = [GpuBuffer(M * N * 2) for _ in range(6)]
+        for o in outs:
+            plan.run(dA, dB, o)
+        nat.call("b200_device_synchronize")
+        plan.status()
+        first = np.empty((M, N), np.uint16)
+        outs[0].copy_to_host(first)
+        check(first, inp, "bf16", "bf16")
+        for o in outs[1:]:
+            got = np.empty((M, N), np.uint16)
+            o.copy_to_host(got)
+            assert np.array_equal(got, first)
+        for b in (dA, dB, *outs):
+            b.free()
 
     def test_deep_rings_and_other_types(self, gpu):
         plan = GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64)
