@@ -3,16 +3,17 @@
 Mirrors the reference's ``aster.execution.core`` (python/aster/execution/core.py:59-717) name
 for name -- ``GpuBuffer``, ``GpuStream``, ``GpuEvent``, ``MemoryManager``, ``InputArray`` /
 ``OutputArray`` / ``InOutArray``, the ``_TimedLaunch`` protocol -- on top of the C ABI instead
-of a nanobind HIP module.  Where the reference loads an HSACO and launches a named kernel
-(``execute_hsaco``), :func:`execute_launch` times any callable that enqueues work on the
-default stream, so the GEMM plan and the bandwidth kernels share one loop.
+of a nanobind HIP module.  :func:`execute_hsaco` keeps the reference's signature: the artifact
+path and the kernel name select one of the library's kernels (there is no code object to load),
+and the upload / timed-launch / download loop is :func:`execute_launch`, which times any
+callable that enqueues work on the default stream.
 """
 
 from __future__ import annotations
 
 import ctypes as C
 import dataclasses
-from typing import Any, Callable, List, Optional
+from typing import Any, Callable, List, Optional, Tuple
 
 import numpy as np
 
@@ -329,3 +330,152 @@ def execute_launch(
         if owns_mm:
             mm.release_all()
     return times_ns
+
+
+# ---------------------------------------------------------------------------------------------
+# execute_hsaco: the reference's entry point, kernel chosen by name
+# ---------------------------------------------------------------------------------------------
+def _host_array(arg) -> np.ndarray:
+    if isinstance(arg, (InputArray, OutputArray, InOutArray)):
+        return arg.array
+    raise TypeError(f"expected an array argument, got {type(arg).__name__}")
+
+
+def _elementwise_launcher(entry_i32: Optional[str], entry_f32: str):
+    def build(_artifact: Optional[dict], arguments: list):
+        arrays = [_host_array(a) for a in arguments[:3]]
+        if len(arrays) != 3 or len({a.size for a in arrays}) != 1:
+            raise ValueError("expected three arrays of equal size: two inputs and the output")
+        dt = arrays[0].dtype
+        if any(a.dtype != dt for a in arrays):
+            raise TypeError("the three arrays must share one dtype")
+        if dt == np.int32 and entry_i32 is not None:
+            entry = entry_i32
+        elif dt == np.float32:
+            entry = entry_f32
+        else:
+            raise TypeError(f"unsupported element type {dt}")
+        n = arrays[0].size
+
+        def launch(a, b, c, *_scalars):
+            nat.call(entry, a.ptr, b.ptr, c.ptr, n, None)
+
+        return launch
+
+    return build
+
+
+def _copy_2d_padded_launcher(artifact: Optional[dict], arguments: list):
+    src, dst = _host_array(arguments[0]), _host_array(arguments[1])
+    if src.ndim != 2 or src.shape != dst.shape or src.dtype != np.float32 or dst.dtype != np.float32:
+        raise ValueError("copy_2d_padded expects two float32 arrays of one 2-D shape")
+    m, n = src.shape
+    depth = int((artifact or {}).get("depth", 2))
+
+    def launch(s, d, *_scalars):
+        nat.call("b200_copy_2d_padded_f32", s.ptr, d.ptr, m, n, depth, 0, None)
+
+    return launch
+
+
+def _gemm_launcher(artifact: Optional[dict], arguments: list):
+    from .gemm import GemmPlan
+
+    if not artifact or "plan" not in artifact:
+        raise RuntimeError("gemm_multitile needs the plan artifact that compile_multitile_gemm wrote as its hsaco_path")
+    kw = dict(artifact["plan"])
+    if kw.get("b_layout", "row_major") != "row_major":
+        raise RuntimeError("execute_hsaco runs row-major B; direct-B configs go through execute_multitile_hsaco, which packs B first")
+    plan = GemmPlan(**kw)
+    res = plan.resources()
+    ws_bytes = res.workspace_bytes or res.optional_workspace_bytes
+    ws = GpuBuffer(ws_bytes) if ws_bytes else None
+
+    def launch(a, b, c, *_scalars):
+        plan.run(a, b, c, workspace=ws)
+
+    def finish():
+        try:
+            plan.status()
+        finally:
+            if ws is not None:
+                ws.free()
+            plan.destroy()
+
+    launch.finish = finish
+    return launch
+
+
+# kernel name -> builder(artifact dict or None, normalised arguments) -> launch callable.
+# The names are the reference's: "kernel" is examples/03_vector_add (run.py:26), "copy_2d_padded"
+# examples/06_copy_layout (copy_2d_padded.py:26), "fused" examples/07_simple_fusion
+# (simple_fusion.py:27), "gemm_multitile" the GEMM generators (test_102_..._lds_cdna3.py:571-579).
+HSACO_KERNELS = {
+    "kernel": _elementwise_launcher("b200_vector_add_i32", "b200_vector_add_f32"),
+    "vector_add": _elementwise_launcher("b200_vector_add_i32", "b200_vector_add_f32"),
+    "fused": _elementwise_launcher(None, "b200_add_relu_f32"),
+    "add_relu": _elementwise_launcher(None, "b200_add_relu_f32"),
+    "copy_2d_padded": _copy_2d_padded_launcher,
+    "gemm_multitile": _gemm_launcher,
+}
+
+
+def _read_artifact(path: Optional[str]) -> Optional[dict]:
+    """The JSON artifact at ``path`` if there is one (the GEMM plan; optional parameters such as
+    ``{"depth": 4}`` for the bandwidth kernels); any other file -- e.g. a real HSACO of the
+    reference -- carries nothing this library can use and is ignored."""
+    import json
+    import os
+
+    if not path or not os.path.isfile(path):
+        return None
+    try:
+        with open(path) as f:
+            art = json.load(f)
+    except (OSError, UnicodeDecodeError, ValueError):
+        return None
+    return art if isinstance(art, dict) else None
+
+
+def execute_hsaco(
+    hsaco_path: Optional[str],
+    kernel_name: str,
+    arguments: list,
+    grid_dim: Tuple[int, int, int] = (1, 1, 1),
+    block_dim: Tuple[int, int, int] = (64, 1, 1),
+    cluster_dim: Optional[Tuple[int, int, int]] = None,
+    num_iterations: int = 1,
+    device_id: Optional[int] = None,
+    flush_llc: Optional[Any] = None,
+    verify_fn: Optional[Callable] = None,
+    memory_manager: Optional[MemoryManager] = None,
+) -> List[int]:
+    """The reference's execution entry point (python/aster/execution/core.py:605-717), same
+    signature and return value: upload the arguments, launch ``kernel_name`` ``num_iterations``
+    times with an event pair and a synchronise around each launch, copy outputs back after the
+    first iteration, call ``verify_fn(arguments)``, return the times in nanoseconds.
+
+    There is no code object to load here: ``kernel_name`` selects one of the library's kernels
+    (:data:`HSACO_KERNELS`) and ``hsaco_path`` names its artifact -- the plan that
+    ``compile_multitile_gemm`` wrote for ``"gemm_multitile"``, optional for the bandwidth
+    kernels.  ``grid_dim``, ``block_dim`` and ``cluster_dim`` are accepted and ignored: every
+    kernel sizes its own persistent grid.  Argument wrappers, raw arrays (in/out) and scalars
+    are handled as in the reference; scalars are passed through to kernels that take none.
+    """
+    try:
+        build = HSACO_KERNELS[kernel_name]
+    except KeyError:
+        raise RuntimeError(f"no kernel named {kernel_name!r} in this library (known: {sorted(HSACO_KERNELS)})") from None
+    if device_id is None:
+        nat.init_current()
+    else:
+        nat.call("b200_init", device_id)
+    normalised = [InOutArray(a) if isinstance(a, np.ndarray) else a for a in arguments]
+    launch = build(_read_artifact(hsaco_path), normalised)
+    try:
+        return execute_launch(launch, arguments, num_iterations=num_iterations, device_id=device_id, flush_llc=flush_llc,
+                              verify_fn=verify_fn, memory_manager=memory_manager)
+    finally:
+        finish = getattr(launch, "finish", None)
+        if finish is not None:
+            finish()

@@ -186,3 +186,14 @@ BENCH_HOOKS = {
     "post_compile_filter": _post_compile_filter,
 }
 BENCH_HOOKS_DIRECT_B = dict(BENCH_HOOKS, bench_label="bench_perf_102_gemm_multitile_directb_sm100", from_label=_from_label_direct_b)
+
+
+def hooks_for_bench(bench: str):
+    """The hooks dict behind a registry's bench name, or ``None``.  Benches of other element
+    types share the hooks of their family under a suffixed name (``..._fp8``, ``..._bf8``,
+    ``..._i8``): a label carries its own element types."""
+    for hooks in (BENCH_HOOKS, BENCH_HOOKS_DIRECT_B):
+        base = hooks["bench_label"]
+        if bench == base or (bench.startswith(base + "_") and bench[len(base) + 1:] in ("fp8", "bf8", "i8")):
+            return dict(hooks, bench_label=bench)
+    return None

@@ -17,6 +17,7 @@ CLI::
     python -m aster_b200.perf_tools update --input results.jsonl --best-known-file reg.json [--apply]
     python -m aster_b200.perf_tools dashboard --measurements results.jsonl --best-known-file reg.json
     python -m aster_b200.perf_tools dashboard --dry-run --best-known-file reg.json
+    python -m aster_b200.perf_tools evaluate --best-known-file reg.json --out results.jsonl
 """
 
 from __future__ import annotations
@@ -223,6 +224,87 @@ def render_dashboard(rows: list[Row], dry_run: bool = False, regress_margin: flo
 # ---------------------------------------------------------------------------------------------
 # CLI
 # ---------------------------------------------------------------------------------------------
+# ---------------------------------------------------------------------------------------------
+# re-measuring the registry
+# ---------------------------------------------------------------------------------------------
+def iter_registry(data: dict, mcpu_filter: Optional[str] = None, bench_filter: Optional[str] = None):
+    """``(mcpu, bench, size_key, slot)`` for every stored slot that passes the filters."""
+    for mcpu, benches in sorted(data.items()):
+        if mcpu_filter and mcpu != mcpu_filter:
+            continue
+        for bench, sizes in sorted(benches.items()):
+            if bench_filter and bench != bench_filter:
+                continue
+            for key, slot in sorted(sizes.items()):
+                yield mcpu, bench, key, slot
+
+
+def collect_todo(data: dict, mcpu_filter: Optional[str] = None, bench_filter: Optional[str] = None) -> dict:
+    """``{(mcpu, bench): [label, ...]}`` for every stored config (tools/perf_evaluate.py:42-51)."""
+    todo: dict = {}
+    for mcpu, bench, _key, slot in iter_registry(data, mcpu_filter, bench_filter):
+        for entry in slot:
+            todo.setdefault((mcpu, bench), []).append(entry["label"])
+    return todo
+
+
+def measure_all(data: dict, out_path: str, *, mcpu_filter: Optional[str] = None, bench_filter: Optional[str] = None,
+                iterations: Optional[int] = None, compile_workers: Optional[int] = None, hsaco_dir: Optional[str] = None,
+                num_gpus: Optional[int] = None, compile_only: bool = False, hooks_for=None, sweep_fn=None, verify_fn=None, log=None) -> str:
+    """Re-measure every label of the registry, bench by bench, and write one result line per
+    config that also passes verification (tools/perf_evaluate.py:54-149): truncate ``out_path``;
+    per ``(mcpu, bench)`` rebuild the configs through the bench's ``from_label`` hook, run the
+    pipelined sweep, verify every measured config on the GPUs, append only the verified ones.
+    ``hooks_for(bench) -> BENCH_HOOKS dict or None``, ``sweep_fn`` and ``verify_fn`` default to
+    the library's own (:func:`aster_b200.multitile_gemm.hooks_for_bench`,
+    :func:`aster_b200.bench_workers.bench_perf_sweep_pipelined`, ``verify_top_configs``)."""
+    from .bench_harness import emit_one_result
+
+    if log is None:
+        log = lambda *a: print(*a, file=sys.stderr)  # noqa: E731
+    if hooks_for is None:
+        from .multitile_gemm import hooks_for_bench as hooks_for
+    if sweep_fn is None or verify_fn is None:
+        from . import bench_workers as bw
+
+        sweep_fn = sweep_fn or bw.bench_perf_sweep_pipelined
+        verify_fn = verify_fn or bw.verify_top_configs
+    open(out_path, "w").close()  # truncate
+    todo = collect_todo(data, mcpu_filter, bench_filter)
+    log(f"=== measure_all: {sum(len(v) for v in todo.values())} stored config(s) across {len(todo)} bench group(s) -> {out_path} ===")
+    for i, ((mcpu, bench), labels) in enumerate(sorted(todo.items()), start=1):
+        log(f"  [{i}/{len(todo)}] {bench} (mcpu={mcpu}, {len(labels)} label(s))")
+        hooks = hooks_for(bench)
+        if hooks is None:
+            log(f"    SKIP -- no hooks known for bench {bench!r}")
+            continue
+        try:
+            configs = [hooks["from_label"](lbl, mcpu) for lbl in labels]
+        except Exception as e:
+            log(f"    SKIP -- a stored label does not parse: {e}")
+            continue
+        per_bench_dir = os.path.join(hsaco_dir, bench) if hsaco_dir else None
+        if per_bench_dir:
+            os.makedirs(per_bench_dir, exist_ok=True)
+        results, paths = sweep_fn(configs, hooks["compile_fn"], hooks["repro_cmd_fn"], mcpu=mcpu, bench=hooks["bench_label"],
+                                  num_gpus=0 if compile_only else num_gpus, compile_workers=compile_workers,
+                                  post_compile_filter=hooks["post_compile_filter"], iterations=iterations, hsaco_dir=per_bench_dir,
+                                  results_file=None)  # lines are written after verification, not during the sweep
+        verified: set = set()
+        if results and not compile_only:
+            ranked = sorted(results, key=lambda r: -(r[1].p50_tf if r[1] is not None else 0.0))
+            verified = verify_fn(ranked, paths, top_n=len(ranked), num_gpus=num_gpus if num_gpus is not None else 1)
+        if verified:
+            with open(out_path, "a") as rs:
+                for cfg, stats in results:
+                    if stats is not None and cfg.label in verified:
+                        emit_one_result(rs, hooks["bench_label"], cfg, stats)
+            log(f"    Emitted {len(verified)}/{len(configs)} verified result(s)")
+        elif not compile_only:
+            log(f"    WARNING: 0/{len(configs)} configs passed correctness for {bench}")
+    return out_path
+
+
 def _read_records(paths: list[str]) -> list[BenchResultRecord]:
     out = []
     for p in paths:
@@ -245,8 +327,22 @@ def main(argv=None) -> int:
     da.add_argument("--dry-run", action="store_true")
     da.add_argument("--regress-margin", type=float, default=DEFAULT_REGRESS_MARGIN)
     da.add_argument("--improve-margin", type=float, default=DEFAULT_IMPROVE_MARGIN)
+    ev = sub.add_parser("evaluate", help="re-measure every stored label on the GPUs; only verified results are written")
+    ev.add_argument("--best-known-file", default=str(DEFAULT_REGISTRY))
+    ev.add_argument("--out", required=True, help="result lines (BENCH_RESULT_JSON) are written here")
+    ev.add_argument("--mcpu", default=None)
+    ev.add_argument("--bench", default=None)
+    ev.add_argument("--iterations", type=int, default=None)
+    ev.add_argument("--compile-workers", type=int, default=None)
+    ev.add_argument("--hsaco-dir", default=None)
+    ev.add_argument("--num-gpus", type=int, default=None)
+    ev.add_argument("--compile-only", action="store_true")
     args = ap.parse_args(argv)
     registry = load_registry(args.best_known_file)
+    if args.cmd == "evaluate":
+        measure_all(registry, args.out, mcpu_filter=args.mcpu, bench_filter=args.bench, iterations=args.iterations,
+                    compile_workers=args.compile_workers, hsaco_dir=args.hsaco_dir, num_gpus=args.num_gpus, compile_only=args.compile_only)
+        return 0
     if args.cmd == "update":
         changes = merge_results_into_registry(registry, _read_records(args.input), args.top_n)
         for c in changes:

@@ -121,7 +121,7 @@ def draw(rng, shape, dist):
         return rng.uniform(-1.0, 1.0, size=shape).astype(np.float32)
     if dist == "int8":
         return rng.integers(-128, 128, size=shape).astype(np.float32)
-    return rng.standard_normal(size=shape, dtype=np.float32)
+    return rng.standard_normal(size=shape).astype(np.float32)
 
 
 def host_operands(w: dict, rank: int, rows: int):
@@ -907,7 +907,7 @@ def run_bandwidth(args, job: Job, w: dict, name: str, protocol_only: bool = Fals
         dev_out = dc
     else:
         M, N = w["M"], w["N"]
-        src = np.random.default_rng(6 + job.rank).standard_normal((M, N), dtype=np.float32)
+        src = np.random.default_rng(6 + job.rank).standard_normal((M, N), dtype=np.float32)  # drawn in float32: 268 M values
         da, dc = GpuBuffer(src.nbytes), GpuBuffer(src.nbytes)
         da.copy_from_host(src)
         alg_bytes = 8 * M * N

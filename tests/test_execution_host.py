@@ -140,3 +140,18 @@ def test_flush_protocol_runs_before_every_launch(fake):
 def test_system_has_gpu_is_false_without_a_device(monkeypatch):
     monkeypatch.setattr(nat, "device_count", lambda: 0)
     assert ex.system_has_gpu("sm_100a") is False
+
+
+def test_execute_hsaco_keeps_the_reference_signature():
+    """Parameter names, order and defaults of python/aster/execution/core.py:605-617."""
+    import inspect
+
+    from aster_b200.execution import HSACO_KERNELS, execute_hsaco
+
+    params = inspect.signature(execute_hsaco).parameters
+    assert list(params) == ["hsaco_path", "kernel_name", "arguments", "grid_dim", "block_dim", "cluster_dim", "num_iterations",
+                            "device_id", "flush_llc", "verify_fn", "memory_manager"]
+    assert params["grid_dim"].default == (1, 1, 1) and params["block_dim"].default == (64, 1, 1)
+    assert params["num_iterations"].default == 1 and params["cluster_dim"].default is None
+    # the reference's kernel names: examples 03, 06, 07 and the GEMM generators
+    assert {"kernel", "copy_2d_padded", "fused", "gemm_multitile"} <= set(HSACO_KERNELS)

@@ -403,6 +403,48 @@ class TestConfiguredProblems:
         got = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", split_k=-1, tile_n=64)
         check(got, inp, "bf16", "bf16")
 
+    # The plans the benchmark times, at the benchmark's sizes (bench.py WORKLOADS).
+
+    @pytest.mark.parametrize("M", [16, 128])
+    def test_decode_shapes_as_benchmarked(self, gpu, M):
+        """Direct-B (weights packed once), static B, 128-column tiles cut in two K halves that meet
+        in the shared memory of a CTA cluster."""
+        kw = dict(tile_n=128, b_layout="packed", static_b=True)
+        res = GemmPlan(M, 8192, 8192, "bf16", "bf16", **kw).resources()
+        assert (res.tile_n, res.tail_tiles, res.tail_parts, res.tail_exchange, res.grid_ctas) == (128, 64, 2, 2, 128)
+        inp = orc.make_inputs(M, 8192, 8192, "bf16", "uniform", 4)
+        got = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", **kw)
+        check(got, inp, "bf16", "bf16")
+        # the same sums in the same order as the exchange through a lent workspace
+        assert np.array_equal(got, gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", tail_split=True, workspace_exchange=True, **kw))
+
+    def test_bf16_4096_as_benchmarked(self, gpu):
+        """With the optional workspace lent: 34 of the 256 tiles are cut in two K halves."""
+        res = GemmPlan(4096, 4096, 4096, "bf16", "bf16").resources()
+        assert (res.tile_m, res.tile_n, res.cta_group, res.tail_tiles, res.tail_parts, res.tail_exchange) == (256, 256, 2, 34, 2, 1)
+        inp = orc.make_inputs(4096, 4096, 4096, "bf16", "uniform", 1)
+        check(gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", tail_split=True), inp, "bf16", "bf16")
+        check(gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="f32", tail_split=True), inp, "bf16", "f32")
+
+    def test_bf16_8192_rows_sample(self, gpu):
+        inp = orc.make_inputs(8192, 8192, 8192, "bf16", "uniform", 1)
+        got = gemm(inp["A"], inp["B"], dtype_ab="bf16", dtype_c="bf16", tail_split=True)
+        rows = np.sort(np.random.default_rng(0).choice(8192, 512, replace=False))
+        check(got[rows], dict(inp, A=inp["A"][rows]), "bf16", "bf16")
+
+    def test_one_shard_of_the_65536_row_problem(self, gpu):
+        """Rank 3 of 8 of the M = 65536, N = K = 8192 problem: rows 24576..32767 of the global A
+        (drawn block-wise so that every world size sees the same matrix), all of B."""
+        from aster_b200.sharding import shard_rows, sharded_uniform_rows
+
+        first, rows = shard_rows(65536, 8, 3)
+        assert (first, rows) == (24576, 8192)
+        a = orc.encode(sharded_uniform_rows(4, first, rows, 8192, threads=4), "bf16")
+        b = orc.encode(np.random.default_rng(5).uniform(-1.0, 1.0, size=(8192, 8192)).astype(np.float32), "bf16")
+        got = gemm(a, b, dtype_ab="bf16", dtype_c="bf16", tail_split=True)
+        pick = np.sort(np.random.default_rng(0).choice(rows, 512, replace=False))
+        check(got[pick], dict(A=a[pick], B=b, scale_a=None, scale_b=None), "bf16", "bf16")
+
 
 class TestProperties:
     """Size-independent properties, usable where a full oracle pass would be slow."""
