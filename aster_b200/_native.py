@@ -154,6 +154,7 @@ SIGNATURES = {
     "b200_gemm_splitk_noalloc_status": [C.POINTER(C.c_uint32)],
     "b200_status_read": [_P, C.POINTER(C.c_uint32)],
     "b200_gemm_last_sm_mhz": [_P, _FP],
+    "b200_gemm_clock_totals": [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
     "b200_launch_count": [C.POINTER(C.c_int64)],
     "b200_vector_add_i32": [_P, _P, _P, _SZ, _P],
     "b200_vector_add_f32": [_P, _P, _P, _SZ, _P],

@@ -44,6 +44,12 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Drop a 128-byte line from the L2 without writing it back (its contents become undefined):
+// for exchange data that has been consumed and must not cost a DRAM write when it is evicted.
+__device__ __forceinline__ void discard_l2_line(const void* p) {
+  asm volatile("discard.global.L2 [%0], 128;" ::"l"(p) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------

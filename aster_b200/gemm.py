@@ -193,11 +193,25 @@ class GemmPlan:
         nat.call("b200_gemm_last_sm_mhz", self.handle, C.byref(mhz))
         return mhz.value
 
+    def clock_totals(self) -> tuple:
+        """``(SM cycles, nanoseconds, launches)`` summed over all launches of the plan so far
+        (CTA 0 of each launch).  Take it before and after a timed region and use
+        :func:`mean_sm_mhz` on the two readings."""
+        cyc, ns, n = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0)
+        nat.call("b200_gemm_clock_totals", self.handle, C.byref(cyc), C.byref(ns), C.byref(n))
+        return cyc.value, ns.value, n.value
+
     def status(self) -> Sequence[int]:
         """Device status words of the last launch; raises ``B200Error`` (TIMEOUT) if a wait gave up."""
         words = (C.c_uint32 * 4)()
         nat.call("b200_status_read", self.handle, words)
         return list(words)
+
+
+def mean_sm_mhz(before: tuple, after: tuple) -> float:
+    """Average SM clock (MHz) of the launches between two :meth:`GemmPlan.clock_totals` readings."""
+    cycles, ns = after[0] - before[0], after[1] - before[1]
+    return cycles / ns * 1000.0 if ns > 0 else 0.0
 
 
 def gemm_splitk_noalloc(A, B, Cbuf, M: int, N: int, K: int, dtype_ab: str = "bf16", dtype_c: str = "bf16",

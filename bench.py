@@ -166,6 +166,7 @@ class ClockSampler:
     def __init__(self, device: int):
         self.samples = []  # (t, sm_mhz, reasons_mask, power_w)
         self.max_mhz = None
+        self.power_limit_w = None
         self._stop = threading.Event()
         self._thread = None
         self._h = None
@@ -178,6 +179,10 @@ class ClockSampler:
             self._nv = pynvml
             self._h = pynvml.nvmlDeviceGetHandleByPciBusId(nat.device_pci_bus_id(device).encode())
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            try:  # read only: the limit the board enforces on itself
+                self.power_limit_w = pynvml.nvmlDeviceGetEnforcedPowerLimit(self._h) / 1000.0
+            except Exception:
+                self.power_limit_w = None
         except Exception as e:  # NVML missing: report no clocks rather than guess
             log(f"clock sampling unavailable: {e}")
 
@@ -231,6 +236,7 @@ class ClockSampler:
             "sm_max_mhz": self.max_mhz,
             "reasons": sorted(name for bit, name in self.REASONS.items() if mask & bit),
             "power_w_max": max(powers) if powers else None,
+            "power_limit_w": self.power_limit_w,
             "samples": len(inside),
             "window": window,
         }
@@ -393,15 +399,26 @@ def run_reference_arm(args, w: dict, name: str) -> dict:
 # ---------------------------------------------------------------------------------------------
 # timing
 # ---------------------------------------------------------------------------------------------
-def time_steps(job: Job, run_step, steps: int, warmup: int):
+class Timed(tuple):
+    """(max-over-ranks ms, this rank's ms, host t0, host t1) with ``sm_mhz``: the average SM clock
+    of the timed launches as the kernels themselves counted it (0 when no plan was given)."""
+
+    sm_mhz = 0.0
+
+
+def time_steps(job: Job, run_step, steps: int, warmup: int, plan=None):
     """W warm-up steps, then K steps between two events on the default stream; returns
-    (max-over-ranks milliseconds for the K steps, this rank's milliseconds, host t0, host t1)."""
+    (max-over-ranks milliseconds for the K steps, this rank's milliseconds, host t0, host t1).
+    With ``plan`` the result's ``sm_mhz`` is the SM clock averaged over exactly the K timed
+    launches (the plan's cycle and nanosecond totals are read before and after them)."""
     from aster_b200 import _native as nat
     from aster_b200.execution import GpuEvent
+    from aster_b200.gemm import mean_sm_mhz
 
     for i in range(warmup):
         run_step(i)
     nat.call("b200_device_synchronize")
+    before = plan.clock_totals() if plan is not None else None
     job.barrier()
     e0, e1 = GpuEvent(), GpuEvent()
     t0 = time.perf_counter()
@@ -414,27 +431,36 @@ def time_steps(job: Job, run_step, steps: int, warmup: int):
     t1 = time.perf_counter()
     job.barrier()
     ms = e1.elapsed_ms(e0)
-    return job.max_over_ranks(ms), ms, t0, t1
+    out = Timed((job.max_over_ranks(ms), ms, t0, t1))
+    if plan is not None:
+        out.sm_mhz = mean_sm_mhz(before, plan.clock_totals())
+    return out
 
 
-def time_reference_protocol(run_step, launches: int = REF_LAUNCHES, drop: int = REF_DROP) -> dict:
+def time_reference_protocol(run_step, launches: int = REF_LAUNCHES, drop: int = REF_DROP, plan=None) -> dict:
     """The reference's protocol (python/aster/execution/core.py:698-703 and
     bench_harness.py:93-94,181-198): every launch between its own pair of events and followed
-    by a synchronise; the first `drop` are warm-up; statistics over the rest, in ms."""
+    by a synchronise; the first `drop` are warm-up; statistics over the rest, in ms.  With
+    ``plan``, ``sm_mhz`` is the SM clock averaged over the kept launches."""
     from aster_b200.execution import GpuEvent
+    from aster_b200.gemm import mean_sm_mhz
 
     e0, e1 = GpuEvent(), GpuEvent()
     times = []
+    before = None
     for i in range(launches):
+        if i == drop and plan is not None:
+            before = plan.clock_totals()
         e0.record()
         run_step(i)
         e1.record()
         e1.synchronize()
         times.append(e1.elapsed_ms(e0))
+    sm_mhz = mean_sm_mhz(before, plan.clock_totals()) if before is not None else 0.0
     kept = np.sort(np.asarray(times[drop:], dtype=np.float64))
     pct = lambda q: float(kept[min(len(kept) - 1, int(q * len(kept)))])  # noqa: E731
     return {"launches": launches, "dropped": drop, "p50_ms": pct(0.5), "p0_ms": float(kept[0]), "p10_ms": pct(0.1), "p90_ms": pct(0.9),
-            "mean_ms": float(kept.mean()), "stddev_ms": float(kept.std())}
+            "mean_ms": float(kept.mean()), "stddev_ms": float(kept.std()), "sm_mhz": sm_mhz}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -452,7 +478,7 @@ class GemmCase:
         self.w = w
         self.rows = rows = w["M"] // world if w.get("strong") else w["M"]
         self.N, self.K = N, K = w["N"], w["K"]
-        self.plan_kw = {k: w[k] for k in ("epilogue", "split_k", "tile_n", "static_b", "b_layout", "stages", "workspace_exchange") if k in w}
+        self.plan_kw = {k: w[k] for k in ("epilogue", "split_k", "tile_n", "static_b", "b_layout", "stages", "workspace_exchange", "raster_group") if k in w}
         self.plan = plan = GemmPlan(rows, N, K, w["dtype_ab"], w["dtype_c"], **self.plan_kw)
         self.res = res = plan.resources()
         self.ops = ops = host_operands(w, rank, rows)
@@ -578,7 +604,7 @@ def roofline_of(case: GemmCase, ms: float, sustained: bool, sm_mhz: float | None
     if sm_mhz:
         # The tensor pipes' own ceiling at the clock the launch really ran at: SMs x flop/clk x MHz.
         clock_peak = SM_COUNT * FLOP_PER_CLK_PER_SM[1 if eight else 2] * sm_mhz * 1e6 / 1e12
-        out["sm_mhz_in_kernel"] = sm_mhz
+        out["sm_mhz_in_kernel"] = sm_mhz  # SM cycles / nanoseconds counted by the timed launches themselves
         out["frac_of_clock_peak"] = achieved / clock_peak
     return out
 
@@ -659,7 +685,7 @@ def run_e2e(args, job: Job, case: GemmCase, out_device: np.ndarray) -> dict:
 
     w, ops, plan = case.w, case.ops, case.plan
     numa = bind_to_gpu_numa_node(job.local_rank) if job.dist is not None else None
-    if plan.direct_b:
+    if plan.direct_b or case.plan_kw.get("static_b"):  # B arrives from the host every step here: neither packed nor static
         plan = GemmPlan(case.rows, case.N, case.K, w["dtype_ab"], w["dtype_c"], **{k: v for k, v in case.plan_kw.items() if k not in ("b_layout", "static_b")})
     kw = dict(depth=2, bias=ops["bias"], scale_a=ops["scale_a"], scale_b=ops["scale_b"])
     sharded_b = job.dist is not None and job.world > 1 and case.N % job.world == 0
@@ -705,10 +731,11 @@ def run_gemm(args, job: Job, w: dict, name: str) -> tuple:
     sampler = ClockSampler(job.local_rank)
     sampler.start()
     launches0 = nat.launch_count()
-    ms_total, ms_rank, t0, t1 = time_steps(job, case.run_step, args.steps, args.warmup)
+    timed = time_steps(job, case.run_step, args.steps, args.warmup, plan=plan)
+    ms_total, ms_rank, t0, t1 = timed
     launches = (nat.launch_count() - launches0) - args.warmup * case.launches_per_step
     plan.status()
-    mhz = plan.last_sm_mhz()
+    mhz = timed.sm_mhz  # averaged over the K timed launches
     clocks = sampler.summary(t0, t1)
 
     out = case.result(args.warmup + args.steps - 1)
@@ -743,7 +770,7 @@ def run_gemm(args, job: Job, w: dict, name: str) -> tuple:
     }
     if job.dist is not None:
         line["per_rank"] = {"ms_per_step": [t / args.steps for t in job.gather_floats(ms_rank)], "sm_mhz_in_kernel": job.gather_floats(mhz),
-                            "note": "value uses the slowest rank's time; in-kernel MHz = SM cycles / ns of CTA 0 of the last launch"}
+                            "note": "value uses the slowest rank's time; in-kernel MHz = SM cycles / ns of CTA 0, summed over the timed launches"}
         if w["dtype_c"] == "bf16":
             line["allgather"] = time_allgather(job, case.sets[0][2], rows, N)
     if world == 1 and job.rank == 0 and not args.no_cpu_baseline:
@@ -762,9 +789,10 @@ def run_sustained(job: Job, case: GemmCase, ms_hint: float, target_ms: float = 4
     steps = int(min(20000, max(50, target_ms / max(ms_hint, 1e-3))))
     sampler = ClockSampler(job.local_rank)
     sampler.start()
-    ms_total, ms_rank, t0, t1 = time_steps(job, case.run_step, steps, 3)
+    timed = time_steps(job, case.run_step, steps, 3, plan=case.plan)
+    ms_total, ms_rank, t0, t1 = timed
     case.plan.status()
-    mhz = case.plan.last_sm_mhz()
+    mhz = timed.sm_mhz
     clocks = sampler.summary(t0, t1)
     sampler.stop()
     inside = [s[1] for s in sampler.samples if t0 <= s[0] <= t1]
@@ -797,15 +825,16 @@ def run_gemm_leg(job: Job, w: dict, name: str, launches: int = REF_LAUNCHES, dro
             case.run_step(i)
         nat.call("b200_device_synchronize")
         l0 = nat.launch_count()
-        stats = time_reference_protocol(case.run_step, launches, drop)
+        stats = time_reference_protocol(case.run_step, launches, drop, plan=case.plan)
         case.plan.status()
-        mhz = case.plan.last_sm_mhz()
+        mhz = stats["sm_mhz"]
         n_launched = nat.launch_count() - l0
         if stats["p50_ms"] < SHORT_KERNEL_MS:
             back_to_back = max(back_to_back, 300)  # a longer train for kernels of a few tens of microseconds
-        ms_b2b_all, _, _, _ = time_steps(job, case.run_step, back_to_back, 3)
+        timed = time_steps(job, case.run_step, back_to_back, 3, plan=case.plan)
+        ms_b2b_all = timed[0]
         case.plan.status()
-        mhz_b2b = case.plan.last_sm_mhz()
+        mhz_b2b = timed.sm_mhz
         out = case.result(3 + back_to_back - 1)
         check = case.verify(out)
         p50 = job.max_over_ranks(stats["p50_ms"])
@@ -858,9 +887,9 @@ def run_strong(job: Job) -> dict:
             case.run_step(i)
         nat.call("b200_device_synchronize")
         job.barrier()
-        stats = time_reference_protocol(case.run_step, 60, 10)
+        stats = time_reference_protocol(case.run_step, 60, 10, plan=case.plan)
         case.plan.status()
-        mhz = case.plan.last_sm_mhz()
+        mhz = stats["sm_mhz"]
         ms_b2b, _, _, _ = time_steps(job, case.run_step, 20, 3)
         out = case.result(3 + 20 - 1)
         check = case.verify(out)

@@ -229,6 +229,12 @@ int b200_status_read(b200_gemm_plan* plan, uint32_t words[4]);
  * CTA 0 spent in the kernel (synchronises the device).  0 if the plan was never launched.
  * Per-launch tracing in the spirit of the reference's s_memtime cycle counters (README.md:273). */
 int b200_gemm_last_sm_mhz(b200_gemm_plan* plan, float* mhz);
+/* The same two counters summed over every launch of the plan so far, with the number of
+ * launches (synchronises the device).  Differences taken around a timed region give the average
+ * SM clock of exactly the launches that were timed: cycles / nanoseconds * 1000 = MHz.  (A burst
+ * of launches starts at a high clock and sinks towards what the power cap allows, so the last
+ * launch alone reads lower than the burst's average.) */
+int b200_gemm_clock_totals(b200_gemm_plan* plan, uint64_t* sm_cycles, uint64_t* nanoseconds, uint64_t* launches);
 /* Number of kernel launches issued by this library on the calling process so far. */
 int b200_launch_count(int64_t* count);
 

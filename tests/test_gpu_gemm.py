@@ -522,6 +522,15 @@ class TestPlanObject:
         assert (tf > 0).all()
         assert plan.time_batch(*bufs, iters=4) > 0
         assert plan.status() == [0, 0, 0, 0]
+        # cycle / nanosecond totals of the launches in between: their average SM clock
+        from aster_b200.gemm import mean_sm_mhz
+
+        before = plan.clock_totals()
+        for _ in range(5):
+            plan.run(*bufs)
+        after = plan.clock_totals()
+        assert after[2] - before[2] == 5 and 300.0 < mean_sm_mhz(before, after) < 2200.0
+        assert 300.0 < plan.last_sm_mhz() < 2200.0
         assert plan.resources().regs_per_thread > 0
         for b in bufs:
             b.free()
