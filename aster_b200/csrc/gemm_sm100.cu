@@ -280,16 +280,23 @@ struct b200_gemm_plan {
   // its shared memory (see gemm::Params::cluster_exchange); needs no workspace.
   bool cluster_exchange = false;
   bool cluster_exchange_ok = true;  // cleared when the device cannot co-schedule the clusters
-  const void* tail_ws_seen = nullptr;  // workspace whose flag area has been zeroed
+  // Workspaces whose flag area has been zeroed (a pipeline alternates between a few).
+  static constexpr int kSeenSlots = 4;
+  const void* tail_ws_seen[kSeenSlots] = {};
+  int tail_ws_next = 0;
   KernelFn kernel = nullptr;
   bool attr_set = false;
   int attr_device = -1;
   uint32_t* status = nullptr;  // device, 8 words, allocated on first run
   int status_device = -1;
-  // Tensor maps are a pure function of (pointer, shape); cache the last pair.
-  const void* map_a_ptr = nullptr;
-  const void* map_b_ptr = nullptr;
-  CUtensorMap map_a, map_b;
+  // Tensor maps are a pure function of (pointer, shape): the last few of each operand are kept, so
+  // that a caller rotating over a few buffers (a host pipeline's slots, operand sets) does not
+  // re-encode on every launch.
+  static constexpr int kMapSlots = 4;
+  const void* map_a_ptr[kMapSlots] = {};
+  const void* map_b_ptr[kMapSlots] = {};
+  CUtensorMap map_a[kMapSlots], map_b[kMapSlots];
+  int map_a_next = 0, map_b_next = 0;
 };
 
 namespace {
@@ -427,10 +434,10 @@ int ensure_device_state(b200_gemm_plan* plan, cudaStream_t stream) {
         size_grid(plan, units_cap);
       }
     }
-    plan->tail_ws_seen = nullptr;
+    for (auto& seen : plan->tail_ws_seen) seen = nullptr;
     plan->attr_set = true;
     plan->attr_device = dev;
-    plan->map_a_ptr = plan->map_b_ptr = nullptr;
+    for (int i = 0; i < b200_gemm_plan::kMapSlots; ++i) plan->map_a_ptr[i] = plan->map_b_ptr[i] = nullptr;
   }
   if (plan->status == nullptr || plan->status_device != dev) {
     if (plan->status != nullptr) cudaFree(plan->status);
@@ -471,20 +478,31 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
                "gemm_run: i32 output carries the integer sums unchanged; scales need f32 or bf16 output");
   B200_REQUIRE(!plan->mx || (plan->sfa != nullptr && plan->sfb != nullptr),
                "gemm_run: a block-scaled plan needs its scales first (b200_gemm_plan_set_mx_scales)");
-  if (plan->map_a_ptr != A) {
-    int rc = make_operand_map(&plan->map_a, A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), static_cast<uint32_t>(plan->am));  // per CTA
-    if (rc != B200_OK) return rc;
-    plan->map_a_ptr = A;
+  int ia = -1, ib = -1;
+  for (int i = 0; i < b200_gemm_plan::kMapSlots; ++i) {
+    if (plan->map_a_ptr[i] == A) ia = i;
+    if (plan->map_b_ptr[i] == B) ib = i;
   }
-  if (plan->map_b_ptr != B) {
+  if (ia < 0) {
+    ia = plan->map_a_next;
+    plan->map_a_ptr[ia] = nullptr;
+    int rc = make_operand_map(&plan->map_a[ia], A, d.dtype_ab, static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.K), static_cast<uint32_t>(plan->am));  // per CTA
+    if (rc != B200_OK) return rc;
+    plan->map_a_ptr[ia] = A;
+    plan->map_a_next = (ia + 1) % b200_gemm_plan::kMapSlots;
+  }
+  if (ib < 0) {
+    ib = plan->map_b_next;
+    plan->map_b_ptr[ib] = nullptr;
     if (direct_b(plan)) {
-      plan->map_b = plan->map_a;  // never dereferenced: packed B is streamed with 1-D bulk copies
+      plan->map_b[ib] = plan->map_a[ia];  // never dereferenced: packed B is streamed with 1-D bulk copies
     } else {
-      int rc = make_operand_map(&plan->map_b, B, d.dtype_ab, static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.K),
+      int rc = make_operand_map(&plan->map_b[ib], B, d.dtype_ab, static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.K),
                                 static_cast<uint32_t>(plan->bn / plan->cg));
       if (rc != B200_OK) return rc;
     }
-    plan->map_b_ptr = B;
+    plan->map_b_ptr[ib] = B;
+    plan->map_b_next = (ib + 1) % b200_gemm_plan::kMapSlots;
   }
   Params p;
   std::memset(&p, 0, sizeof(p));
@@ -533,9 +551,18 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     // so that the next launch outside a graph clears what the replays leave behind.
     cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
     B200_CUDA_OK(cudaStreamIsCapturing(stream, &capturing));
-    if (capturing != cudaStreamCaptureStatusNone || plan->tail_ws_seen != workspace) {
+    int seen = -1;
+    for (int i = 0; i < b200_gemm_plan::kSeenSlots; ++i) {
+      if (plan->tail_ws_seen[i] == workspace) seen = i;
+    }
+    if (capturing != cudaStreamCaptureStatusNone || seen < 0) {
       B200_CUDA_OK(cudaMemsetAsync(workspace, 0, static_cast<size_t>(plan->tail_flag_bytes), stream));
-      plan->tail_ws_seen = capturing != cudaStreamCaptureStatusNone ? nullptr : workspace;
+      if (capturing != cudaStreamCaptureStatusNone) {
+        if (seen >= 0) plan->tail_ws_seen[seen] = nullptr;
+      } else {
+        plan->tail_ws_seen[plan->tail_ws_next] = workspace;
+        plan->tail_ws_next = (plan->tail_ws_next + 1) % b200_gemm_plan::kSeenSlots;
+      }
     }
     p.tail_tiles = plan->tail_tiles;
     p.tail_parts = plan->tail_parts;
@@ -574,7 +601,7 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    B200_CUDA_OK(cudaLaunchKernelEx(&cfg, plan->kernel, plan->map_a, plan->map_b, plan->map_sfa, plan->map_sfb, p));
+    B200_CUDA_OK(cudaLaunchKernelEx(&cfg, plan->kernel, plan->map_a[ia], plan->map_b[ib], plan->map_sfa, plan->map_sfb, p));
   }
   b200::count_launch();
   B200_CUDA_OK(cudaGetLastError());

@@ -158,6 +158,27 @@ def execute_multitile_hsaco(cfg: B200GemmInstance, hsaco_path: str, num_iteratio
     return C_output, times_ns
 
 
+def _as_b200_instance(cfg) -> B200GemmInstance:
+    """A plain ``WeakScaledMappedGemmInstance`` (the older template family's config type) as the
+    executable instance of the same label and operand path."""
+    if isinstance(cfg, B200GemmInstance):
+        return cfg
+    return MultitileGemmInstance.from_label(cfg.label, operand_path=cfg.mapping.operand_path)
+
+
+def compile_gemm(cfg, output_hsaco_path: str, **kw):
+    """``compile_gemm`` of the weak-scaled template family
+    (contrib/kittens/test/test_perf_001_gemm_fp16_weak_scaled.py:181-231): same call, same
+    ``(path, text)`` return; the config may be a plain ``WeakScaledMappedGemmInstance``."""
+    return compile_multitile_gemm(_as_b200_instance(cfg), output_hsaco_path, **kw)
+
+
+def execute_gemm_hsaco(cfg, hsaco_path: str, num_iterations: int, A: np.ndarray, B: np.ndarray, skip_gpu_check: bool = False):
+    """``execute_gemm_hsaco`` of the same family (test_perf_001_...:234-272): row-major A and B in,
+    ``(C_output, times_ns)`` out; a direct-B config has its B preshuffled here."""
+    return execute_multitile_hsaco(_as_b200_instance(cfg), hsaco_path, num_iterations, A, B, skip_gpu_check)
+
+
 def _repro_cmd(cfg) -> str:
     return f"python -m aster_b200.bench_gemm {cfg.label}"
 

@@ -176,6 +176,17 @@ def test_compile_fn_writes_an_artifact(tmp_path, native_lib):
         load_artifact(str(tmp_path / "bad.json"))
 
 
+def test_older_template_family_entry_points(tmp_path, native_lib):
+    """compile_gemm / execute_gemm_hsaco of test_perf_001 accept the plain config type."""
+    from aster_b200.gemm_config import GemmMappingSpec, GemmSpec, WeakScaledMappedGemmInstance
+    from aster_b200.multitile_gemm import compile_gemm, execute_gemm_hsaco  # noqa: F401
+
+    plain = WeakScaledMappedGemmInstance(GemmSpec.from_sizes(256, 256, 128), GemmMappingSpec([2, 2, 1], [2, 2, 1], [4, 4, 1]))
+    path, text = compile_gemm(plain, str(tmp_path / "w.b200plan.json"), num_vgprs=256, num_agprs=256)
+    art = load_artifact(path)
+    assert art["label"].startswith(plain.label) and art["plan"]["M"] == 256 and art["kernel_name"] == "gemm_multitile"
+
+
 def test_nccl_entry_points_check_arguments_without_a_gpu(native_lib):
     """NCCL is opened at run time: with it present the version reads back, without it the call
     says so; argument checks come before any NCCL or CUDA call."""

@@ -159,3 +159,19 @@ def test_gpu_runner_protocol(gpu, tmp_path):
     out = gpu_runner.run({"hsaco_path": "unused.hsaco", "kernel_name": "kernel", "grid": [1, 1, 1], "block": [64, 1, 1],
                           "input_files": [files["a"], files["b"]], "output_files": [files["c"]]})
     assert len(out["times"]) == 1 and np.array_equal(np.load(files["c"]), a + b)
+
+
+def test_weak_scaled_family_compile_and_execute(gpu, tmp_path):
+    """compile_gemm + execute_gemm_hsaco (test_perf_001_gemm_fp16_weak_scaled.py:181-272) on a plain
+    WeakScaledMappedGemmInstance, checked the way that file checks (:358): numpy, rtol = atol = 1e-2."""
+    from aster_b200.gemm_config import GemmMappingSpec, GemmSpec, WeakScaledMappedGemmInstance
+    from aster_b200.multitile_gemm import compile_gemm, execute_gemm_hsaco
+
+    cfg = WeakScaledMappedGemmInstance(GemmSpec.from_sizes(256, 256, 128), GemmMappingSpec([2, 2, 1], [2, 2, 1], [4, 4, 1]))
+    path, _ = compile_gemm(cfg, str(tmp_path / "w.b200plan.json"))
+    np.random.seed(42)
+    A = (np.random.randn(256, 128) * 0.1).astype(np.float16)
+    B = (np.random.randn(256, 128) * 0.1).astype(np.float16)
+    C, times = execute_gemm_hsaco(cfg, path, 2, A, B)
+    assert len(times) == 2
+    np.testing.assert_allclose(C.reshape(256, 256), A.astype(np.float32) @ B.astype(np.float32).T, rtol=1e-2, atol=1e-2)

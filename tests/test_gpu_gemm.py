@@ -657,6 +657,32 @@ class TestSharedKernelInstances:
         check(first, inp, "bf16", "f32")
 
 
+    def test_plan_rotating_over_more_buffers_than_it_caches_maps_for(self, gpu):
+        """A plan keeps the tensor maps of its last few operand addresses; six operand sets taking
+        turns (twice around) must each produce their own product."""
+        from aster_b200.execution import GpuBuffer
+
+        M, N, K = 256, 256, 512
+        plan = GemmPlan(M, N, K, "bf16", "f32", tile_n=128)
+        sets = []
+        for i in range(6):
+            inp = orc.make_inputs(M, N, K, "bf16", "uniform", 20 + i)
+            dA, dB, dC = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes), GpuBuffer(M * N * 4)
+            dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
+            sets.append((inp, dA, dB, dC))
+        for _ in range(2):
+            for inp, dA, dB, dC in sets:
+                dC.zero()
+                plan.run(dA, dB, dC)
+        plan.status()
+        for inp, dA, dB, dC in sets:
+            out = np.empty((M, N), np.float32)
+            dC.copy_to_host(out)
+            check(out, inp, "bf16", "f32")
+            for b in (dA, dB, dC):
+                b.free()
+
+
 class TestSkinnyM:
     """M <= 64: stages hold only 32 or 64 rows of A (more ring slots for B).  Same MMAs in the
     same order as with full A stages, so the results are bit-identical to ``tile_m=128``."""
