@@ -355,6 +355,13 @@ def cpu_threads() -> int:
     return os.cpu_count() or 1
 
 
+def common_config(w: dict, name: str, world: int) -> dict:
+    """The `config` object, identical for both arms: what is computed, not how."""
+    rows = w["M"] // world if w.get("strong") else w["M"]
+    return {"workload": w["text"], "name": name, "per_gpu_shape": [rows, w["N"], w["K"]], "global_rows": rows * world,
+            "parallelism": f"m-row shards x{world}, B replicated, no collective"}
+
+
 def run_reference_arm(args, w: dict, name: str) -> dict:
     """--impl reference: every step is the numpy GEMM on a bounded row sample."""
     use_all_host_threads()
@@ -389,7 +396,7 @@ def run_reference_arm(args, w: dict, name: str) -> dict:
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": w["dtype_ab"], "data": "synthetic", "impl": "reference",
-        "config": {"workload": w["text"], "name": name},
+        "config": common_config(w, name, max(1, args.gpus)),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -754,9 +761,8 @@ def run_gemm(args, job: Job, w: dict, name: str) -> tuple:
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if w.get("strong") else "weak",
         "vs_baseline": None, "dtype": w["dtype_ab"], "data": "synthetic", "impl": "ours",
-        "config": {
-            "workload": w["text"], "name": name, "per_gpu_shape": [rows, N, K], "global_rows": rows * world,
-            "parallelism": f"m-row shards x{world}, B replicated, no collective",
+        "config": common_config(w, name, world),
+        "plan": {
             "tile": [res.tile_m, res.tile_n, res.tile_k], "stages": res.stages, "split_k": res.split_k, "grid_ctas": res.grid_ctas,
             "cta_group": res.cta_group, "tail_split": [res.tail_tiles, res.tail_parts],
             "tail_exchange": {0: "none", 1: "workspace", 2: "cluster shared memory"}[res.tail_exchange], "b_layout": plan.b_layout,
