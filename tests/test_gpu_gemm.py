@@ -476,14 +476,17 @@ class TestBoundedWaits:
     into its time limit, the kernel records which wait gave up and returns normally, the host
     reads B200_ERR_TIMEOUT, and the context (and the plan) stay usable."""
 
-    @pytest.mark.parametrize("cta_group", [1, 2])
-    def test_expired_wait_is_reported_not_hung(self, gpu, cta_group):
+    @pytest.mark.parametrize("cta_group,shape", [(1, (512, 256, 512)), (2, (512, 256, 512)),
+                                                 (1, (16, 1024, 4096))])  # the last: clusters of four that exchange partial sums
+    def test_expired_wait_is_reported_not_hung(self, gpu, cta_group, shape):
         import time
 
         from aster_b200 import _native as nat
         from aster_b200.execution import GpuBuffer
 
-        M, N, K = 512, 256, 512
+        M, N, K = shape
+        if M == 16:
+            assert GemmPlan(M, N, K, "bf16", "f32", cta_group=cta_group, tile_n=128).resources().tail_exchange == 2
         inp = orc.make_inputs(M, N, K, "bf16", "uniform", 3)
         dA, dB, dC = GpuBuffer(inp["A"].nbytes), GpuBuffer(inp["B"].nbytes), GpuBuffer(M * N * 4)
         dA.copy_from_host(inp["A"]), dB.copy_from_host(inp["B"])
@@ -493,8 +496,8 @@ class TestBoundedWaits:
         with pytest.raises(nat.B200Error) as e:
             stuck.status()
         elapsed = time.perf_counter() - t0
-        # whichever role's wait expired first is named: 0x10 producer, 0x20 MMA issuer, 0x30 epilogue
-        assert e.value.status == nat.ERR_TIMEOUT and any(f"code 0x{c:x}" in e.value.message for c in (0x10, 0x20, 0x30))
+        # whichever role's wait expired first is named: 0x10 producer, 0x20 MMA issuer, 0x30 epilogue, 0x32 cluster exchange
+        assert e.value.status == nat.ERR_TIMEOUT and any(f"code 0x{c:x}" in e.value.message for c in (0x10, 0x20, 0x30, 0x32))
         assert 0.04 < elapsed < 2.0
         assert stuck.status() == [0, 0, 0, 0]  # reading clears the words
         # The device and the library are still healthy: the same operands through a normal plan.
