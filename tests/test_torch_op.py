@@ -88,7 +88,8 @@ class TestOnGpu:
         bit for bit -- also for a plan whose last tiles are cut along K, whose ready flags are
         versioned per launch (a replay reuses the recorded version, so each replay clears the
         flags first)."""
-        for M, N, K in [(512, 512, 2048), (384, 640, 256)]:
+        # the last shape: a skinny problem whose K ranges meet in a CTA cluster's shared memory
+        for M, N, K in [(512, 512, 2048), (384, 640, 256), (16, 1024, 4096)]:
             g = torch.Generator(device="cuda").manual_seed(M + K)
             a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
             b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
