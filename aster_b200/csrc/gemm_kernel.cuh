@@ -109,12 +109,14 @@ struct Params {
   // programmatic stream serialisation.  The other bits exist only in bring-up builds
   // (-DB200_BRINGUP) and make the kernel skip work, i.e. return garbage: bits 0-1: 1 = producer
   // signals without copying, 2 = MMA warp commits without multiplying; bit 2: skip the tail-split
-  // exchange; bit 5: the epilogue computes but does not store C; bit 6: 16-byte stores only.
+  // exchange; bit 5: the epilogue computes but does not store C; bit 6: 16-byte stores only; bit 7: no
+  // wait for the previous kernel of the stream.
   int debug_mode;
   unsigned wait_limit_ms;  // limit of every bounded wait; 0 = default
   // Non-zero: nothing that precedes a launch in its stream writes B (a weight matrix), so the
   // producer may request the first ring of B tiles before the previous kernel has completed.
   int static_b;
+  int l2_hints;  // non-zero: A + B + C exceed the L2; see the eviction policies in the kernel
 #ifdef B200_BRINGUP
   // Bring-up aid: when non-null, every CTA writes global-timer readings (ns) of its milestones to
   // timeline[blockIdx.x * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel complete,
@@ -363,17 +365,26 @@ struct OutVec<__nv_bfloat16> {
 };
 
 // Store 32 consecutive outputs of one row.  `vec_ok`: the row segment is 16-byte aligned and
-// entirely inside the matrix; `wide_ok`: it is 32-byte aligned as well.
+// entirely inside the matrix; `wide_ok`: it is 32-byte aligned as well; `evict_first` (wide
+// stores only): the lines are the first to leave the L2.
 template <typename OutT>
-__device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], bool vec_ok, int valid, bool wide_ok = false) {
+__device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], bool vec_ok, int valid, bool wide_ok = false,
+                                            bool evict_first = false) {
+  auto st8 = [&](void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
+    if (evict_first) {
+      sm100::st_global_v8<true>(ptr, a, b, c, d, e, f, g, h);
+    } else {
+      sm100::st_global_v8<false>(ptr, a, b, c, d, e, f, g, h);
+    }
+  };
   if (vec_ok) {
     if constexpr (sizeof(OutT) == 4) {
       if (wide_ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          sm100::st_global_v8(dst + 8 * j, __float_as_uint(x[8 * j]), __float_as_uint(x[8 * j + 1]), __float_as_uint(x[8 * j + 2]),
-                              __float_as_uint(x[8 * j + 3]), __float_as_uint(x[8 * j + 4]), __float_as_uint(x[8 * j + 5]),
-                              __float_as_uint(x[8 * j + 6]), __float_as_uint(x[8 * j + 7]));
+          st8(dst + 8 * j, __float_as_uint(x[8 * j]), __float_as_uint(x[8 * j + 1]), __float_as_uint(x[8 * j + 2]),
+              __float_as_uint(x[8 * j + 3]), __float_as_uint(x[8 * j + 4]), __float_as_uint(x[8 * j + 5]),
+              __float_as_uint(x[8 * j + 6]), __float_as_uint(x[8 * j + 7]));
         }
       } else {
         float4* d4 = reinterpret_cast<float4*>(dst);
@@ -388,8 +399,8 @@ __device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], boo
         w[t] = *reinterpret_cast<uint32_t*>(&h);
       }
       if (wide_ok) {
-        sm100::st_global_v8(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
-        sm100::st_global_v8(dst + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+        st8(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+        st8(dst + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
       } else {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
@@ -472,9 +483,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int first_item = static_cast<int>(blockIdx.x) / CG;    // one work item per CTA (pair) at a time
   const int item_stride = static_cast<int>(gridDim.x) / CG;
 
-  // L2 policies of a pair's operand loads: A (reused across the group's columns of tiles) is the
-  // last to be evicted, B (streams past once per group) the first; with the evict-first stores of
-  // C: bf16 8192^3 695 -> 683 us, fp8 8192^3 and the fused problem -0.5 %, 4096^3 unchanged.
+  // L2 policies of a pair's operand loads when the problem is larger than the L2 (p.l2_hints):
+  // A (reused across the group's columns of tiles) is the last to be evicted, B (streams past once
+  // per group) the first, and C leaves with evict-first stores.  Interleaved runs on one GPU:
+  // bf16 8192^3 679 -> 672 us, 8192x8192x2048 with bias and ReLU 177.9 -> 177.2, fp8 8192^3
+  // unchanged; 4096^3, which fits in the L2, lost 0.4 % with them and runs without.
   [[maybe_unused]] const uint64_t pol_a = l2_policy_evict_last();
   [[maybe_unused]] const uint64_t pol_b = l2_policy_evict_first();
   // B tile of ring slot `stg` for K block `kb_abs` (called by the producer's elected lane).
@@ -489,7 +502,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tma_load_2d(b_dst, &tmap_b, full_bar(stg), k_elem, b_row_);
       }
     } else {
-      tma_load_2d_pair_hint(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_, pol_b);
+      if (p.l2_hints != 0) {
+        tma_load_2d_pair_hint(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_, pol_b);
+      } else {
+        tma_load_2d_pair(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_);
+      }
     }
   };
   // Arm the slot's barrier with the bytes of all copies of the stage (both CTAs' in a pair,
@@ -574,7 +591,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // one may already set itself up behind this one (it waits at this same point).
   if (threadIdx.x == 0) stamp(p, 1);
   griddep_launch_dependents();
-  if (CG == 1 || warp != 0 || p.static_b == 0) griddep_wait();  // the producer of a static-B pair plan waits after its early B requests
+  if (bringup_mode(p, 128)) {
+    // measures what the dependence on the previous kernel costs; only valid when nothing in the stream writes A, B or reads C
+  } else if (CG == 1 || warp != 0 || p.static_b == 0) griddep_wait();  // the producer of a static-B pair plan waits after its early B requests
   if (threadIdx.x == 32) stamp(p, 2);
 
   if (warp == 0) {
@@ -643,7 +662,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tma_load_2d_pair(sf_dst + (1 + q) * kScaleBlockBytes, &tmap_sfb, leader_full, 0, (sfb_blk + q) * p.sf_k_stages + ks);
               }
             }
-            tma_load_2d_pair_hint(a_dst, &tmap_a, leader_full, k_elem, a_row, pol_a);
+            if (p.l2_hints != 0) {
+              tma_load_2d_pair_hint(a_dst, &tmap_a, leader_full, k_elem, a_row, pol_a);
+            } else {
+              tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, a_row);
+            }
             if (!b_requested) issue_b(stage, n_blk, b_row, kb0 + kb);
           }
         }
@@ -943,7 +966,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
               }
               if (row_ok && !bringup_mode(p, 32)) {
-                store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
+                store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok, p.l2_hints != 0);
               }
             }
           }
@@ -1054,7 +1077,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
         }
         if (row_ok && !bringup_mode(p, 32)) {
-          store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
+          store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok, p.l2_hints != 0);
         }
       }
       tc_fence_before_sync();

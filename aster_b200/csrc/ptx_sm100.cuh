@@ -306,14 +306,21 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_format, uint32_t a_
 }
 
 // 32-byte global store (sm_100): half as many store requests as two 16-byte stores, which is
-// what bounds an epilogue whose lanes each write their own row.  C is written once and not read
-// again by the launch, so its lines are marked as the first to leave the L2: a 128 MiB C would
-// otherwise sweep the operands out once per launch.
+// what bounds an epilogue whose lanes each write their own row.  kEvictFirst marks the lines as
+// the first to leave the L2 (an output that the launch does not read again and that would
+// otherwise sweep the operands out).
+template <bool kEvictFirst = false>
 __device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
                                              uint32_t g, uint32_t h) {
-  asm volatile("st.global.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
-               "r"(f), "r"(g), "r"(h)
-               : "memory");
+  if constexpr (kEvictFirst) {
+    asm volatile("st.global.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d),
+                 "r"(e), "r"(f), "r"(g), "r"(h)
+                 : "memory");
+  } else {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f),
+                 "r"(g), "r"(h)
+                 : "memory");
+  }
 }
 
 // Programmatic dependent launch.  `griddep_launch_dependents` lets the next kernel of the stream
