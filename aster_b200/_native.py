@@ -105,7 +105,7 @@ class GemmResources(C.Structure):
         ("tail_tiles", C.c_int32),
         ("tail_parts", C.c_int32),
         ("tail_exchange", C.c_int32),
-        ("l2_hints", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

@@ -116,7 +116,6 @@ struct Params {
   // Non-zero: nothing that precedes a launch in its stream writes B (a weight matrix), so the
   // producer may request the first ring of B tiles before the previous kernel has completed.
   int static_b;
-  int l2_hints;  // non-zero: A + B + C exceed the L2; see the eviction policies in the kernel
 #ifdef B200_BRINGUP
   // Bring-up aid: when non-null, every CTA writes global-timer readings (ns) of its milestones to
   // timeline[blockIdx.x * 16 + slot]: 0 entry, 1 prologue done, 2 previous kernel complete,
@@ -365,26 +364,17 @@ struct OutVec<__nv_bfloat16> {
 };
 
 // Store 32 consecutive outputs of one row.  `vec_ok`: the row segment is 16-byte aligned and
-// entirely inside the matrix; `wide_ok`: it is 32-byte aligned as well; `evict_first` (wide
-// stores only): the lines are the first to leave the L2.
+// entirely inside the matrix; `wide_ok`: it is 32-byte aligned as well.
 template <typename OutT>
-__device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], bool vec_ok, int valid, bool wide_ok = false,
-                                            bool evict_first = false) {
-  auto st8 = [&](void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
-    if (evict_first) {
-      sm100::st_global_v8<true>(ptr, a, b, c, d, e, f, g, h);
-    } else {
-      sm100::st_global_v8<false>(ptr, a, b, c, d, e, f, g, h);
-    }
-  };
+__device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], bool vec_ok, int valid, bool wide_ok = false) {
   if (vec_ok) {
     if constexpr (sizeof(OutT) == 4) {
       if (wide_ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          st8(dst + 8 * j, __float_as_uint(x[8 * j]), __float_as_uint(x[8 * j + 1]), __float_as_uint(x[8 * j + 2]),
-              __float_as_uint(x[8 * j + 3]), __float_as_uint(x[8 * j + 4]), __float_as_uint(x[8 * j + 5]),
-              __float_as_uint(x[8 * j + 6]), __float_as_uint(x[8 * j + 7]));
+          sm100::st_global_v8(dst + 8 * j, __float_as_uint(x[8 * j]), __float_as_uint(x[8 * j + 1]), __float_as_uint(x[8 * j + 2]),
+                              __float_as_uint(x[8 * j + 3]), __float_as_uint(x[8 * j + 4]), __float_as_uint(x[8 * j + 5]),
+                              __float_as_uint(x[8 * j + 6]), __float_as_uint(x[8 * j + 7]));
         }
       } else {
         float4* d4 = reinterpret_cast<float4*>(dst);
@@ -399,8 +389,8 @@ __device__ __forceinline__ void store_row32(OutT* dst, const float (&x)[32], boo
         w[t] = *reinterpret_cast<uint32_t*>(&h);
       }
       if (wide_ok) {
-        st8(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
-        st8(dst + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+        sm100::st_global_v8(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+        sm100::st_global_v8(dst + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
       } else {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
@@ -483,13 +473,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int first_item = static_cast<int>(blockIdx.x) / CG;    // one work item per CTA (pair) at a time
   const int item_stride = static_cast<int>(gridDim.x) / CG;
 
-  // L2 policies of a pair's operand loads when the problem is larger than the L2 (p.l2_hints):
-  // A (reused across the group's columns of tiles) is the last to be evicted, B (streams past once
-  // per group) the first, and C leaves with evict-first stores.  Interleaved runs on one GPU:
-  // bf16 8192^3 679 -> 672 us, 8192x8192x2048 with bias and ReLU 177.9 -> 177.2, fp8 8192^3
-  // unchanged; 4096^3, which fits in the L2, lost 0.4 % with them and runs without.
-  [[maybe_unused]] const uint64_t pol_a = l2_policy_evict_last();
-  [[maybe_unused]] const uint64_t pol_b = l2_policy_evict_first();
   // B tile of ring slot `stg` for K block `kb_abs` (called by the producer's elected lane).
   auto issue_b = [&](int stg, int n_blk_, int b_row_, int kb_abs) {
     const uint32_t b_dst = smem_base + stg * kStageBytes + kABytes;
@@ -502,11 +485,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tma_load_2d(b_dst, &tmap_b, full_bar(stg), k_elem, b_row_);
       }
     } else {
-      if (p.l2_hints != 0) {
-        tma_load_2d_pair_hint(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_, pol_b);
-      } else {
-        tma_load_2d_pair(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_);
-      }
+      tma_load_2d_pair(b_dst, &tmap_b, map_to_cta(full_bar(stg), 0u), k_elem, b_row_);
     }
   };
   // Arm the slot's barrier with the bytes of all copies of the stage (both CTAs' in a pair,
@@ -662,11 +641,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tma_load_2d_pair(sf_dst + (1 + q) * kScaleBlockBytes, &tmap_sfb, leader_full, 0, (sfb_blk + q) * p.sf_k_stages + ks);
               }
             }
-            if (p.l2_hints != 0) {
-              tma_load_2d_pair_hint(a_dst, &tmap_a, leader_full, k_elem, a_row, pol_a);
-            } else {
-              tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, a_row);
-            }
+            tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, a_row);
             if (!b_requested) issue_b(stage, n_blk, b_row, kb0 + kb);
           }
         }
@@ -966,7 +941,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
               }
               if (row_ok && !bringup_mode(p, 32)) {
-                store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok, p.l2_hints != 0);
+                store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
               }
             }
           }
@@ -1077,7 +1052,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
         }
         if (row_ok && !bringup_mode(p, 32)) {
-          store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok, p.l2_hints != 0);
+          store_row32<OutT>(C + static_cast<size_t>(row) * p.N + col0, x, n_vec_ok && valid == 32, valid, n_wide_ok);
         }
       }
       tc_fence_before_sync();

@@ -170,7 +170,6 @@ int mma_kind_for(int dtype_ab) { return dtype_ab == B200_I8 ? sm100::kKindI8 : (
 
 constexpr int kMaxSmemOptin = 232448;  // 227 KB: the sm_100 per-block opt-in limit
 constexpr int kDefaultSms = 148;
-constexpr int kDefaultL2Bytes = 126 << 20;  // until the device has been asked
 
 // Packs B into the shared-memory image of each (n block, k block) tile: BN rows of 128 bytes,
 // 16-byte chunk c of row r stored at chunk position c ^ (r % 8) (the 128-byte swizzle), tiles
@@ -265,7 +264,6 @@ struct b200_gemm_plan {
   int split_k = 1;
   int grid = 0;
   int sm_count = kDefaultSms;
-  bool l2_hints = false;  // A + B + C exceed the L2: eviction priorities on a pair's loads and on the C stores
   int smem = 0;
   int eb_ab = 2;
   int kb_elems = 64;
@@ -302,14 +300,6 @@ struct b200_gemm_plan {
 };
 
 namespace {
-
-// Eviction priorities in the L2 (see gemm::Params::l2_hints) only pay when the operands and the
-// result together do not fit in it.
-bool wants_l2_hints(const b200_gemm_plan* plan, int l2_bytes) {
-  const b200_gemm_desc& d = plan->desc;
-  const double footprint = (static_cast<double>(d.M) + d.N) * d.K * plan->eb_ab + static_cast<double>(d.M) * d.N * elt_bytes(d.dtype_c);
-  return plan->cg == 2 && footprint > static_cast<double>(l2_bytes);
-}
 
 bool direct_b(const b200_gemm_plan* p) { return p->desc.b_layout != B200_B_ROW_MAJOR_NK; }
 
@@ -399,9 +389,6 @@ int ensure_device_state(b200_gemm_plan* plan, cudaStream_t stream) {
     int sms = kDefaultSms;
     B200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     plan->sm_count = sms;
-    int l2_bytes = 0;
-    B200_CUDA_OK(cudaDeviceGetAttribute(&l2_bytes, cudaDevAttrL2CacheSize, dev));
-    plan->l2_hints = wants_l2_hints(plan, l2_bytes);
     int cap = plan->desc.max_ctas > 0 ? plan->desc.max_ctas : sms;
     int units_cap = cap;
     if (plan->cg == 2) {
@@ -547,7 +534,6 @@ int launch(b200_gemm_plan* plan, const void* A, const void* B, void* C, const fl
   p.timeline = plan->timeline;
 #endif
   p.static_b = (d.reserved[1] & 2) != 0 ? 1 : 0;
-  p.l2_hints = plan->l2_hints ? 1 : 0;
   p.debug_mode = d.reserved[0];
   p.wait_limit_ms = d.reserved[2] > 0 ? static_cast<unsigned>(d.reserved[2]) : 0u;
   if (plan->tail_parts > 1 && plan->cluster_exchange) {
@@ -725,7 +711,6 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
     if (cg == 2 && !mx && (k_blocks <= 8 || (k_blocks <= 64 && wide_tiles > kDefaultSms / 2 && wide_tiles <= kDefaultSms))) cg = 1;
   }
   plan->cg = cg;
-  plan->l2_hints = wants_l2_hints(plan, kDefaultL2Bytes);
   plan->mx = mx;
   plan->m_blocks = ceil_div(d.M, gemm::kBM * cg);
 
@@ -861,7 +846,6 @@ int b200_gemm_plan_resources(const b200_gemm_plan* plan, b200_gemm_resources* ou
   out->tail_tiles = plan->tail_tiles;
   out->tail_parts = plan->tail_parts;
   out->tail_exchange = plan->tail_parts > 1 ? (plan->cluster_exchange ? 2 : 1) : 0;
-  out->l2_hints = plan->l2_hints ? 1 : 0;
   // Registers per thread come from the loaded function; without a device this stays -1.
   out->regs_per_thread = -1;
   cudaFuncAttributes fa;

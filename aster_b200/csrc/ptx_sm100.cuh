@@ -155,26 +155,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* 
       "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
-// L2 eviction policies for the hinted loads below: the rows of A of the current group of tile
-// rows are reused by every column of tiles and should stay; B streams past once per group.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-// The pair load with an L2 cache hint.
-__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const void* tmap, uint32_t bar, int c0, int c1, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(
-          smem_dst),
-      "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
-      : "memory");
-}
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
@@ -306,21 +286,12 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_format, uint32_t a_
 }
 
 // 32-byte global store (sm_100): half as many store requests as two 16-byte stores, which is
-// what bounds an epilogue whose lanes each write their own row.  kEvictFirst marks the lines as
-// the first to leave the L2 (an output that the launch does not read again and that would
-// otherwise sweep the operands out).
-template <bool kEvictFirst = false>
+// what bounds an epilogue whose lanes each write their own row.
 __device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
                                              uint32_t g, uint32_t h) {
-  if constexpr (kEvictFirst) {
-    asm volatile("st.global.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d),
-                 "r"(e), "r"(f), "r"(g), "r"(h)
-                 : "memory");
-  } else {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f),
-                 "r"(g), "r"(h)
-                 : "memory");
-  }
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h)
+               : "memory");
 }
 
 // Programmatic dependent launch.  `griddep_launch_dependents` lets the next kernel of the stream

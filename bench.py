@@ -764,7 +764,7 @@ def run_gemm(args, job: Job, w: dict, name: str) -> tuple:
         "config": common_config(w, name, world),
         "plan": {
             "tile": [res.tile_m, res.tile_n, res.tile_k], "stages": res.stages, "split_k": res.split_k, "grid_ctas": res.grid_ctas,
-            "cta_group": res.cta_group, "tail_split": [res.tail_tiles, res.tail_parts], "l2_eviction_hints": bool(res.l2_hints),
+            "cta_group": res.cta_group, "tail_split": [res.tail_tiles, res.tail_parts],
             "tail_exchange": {0: "none", 1: "workspace", 2: "cluster shared memory"}[res.tail_exchange], "b_layout": plan.b_layout,
             "l2": f"rotating {case.n_sets} operand sets ({case.n_sets * case.set_bytes / 2**20:.0f} MiB) > {L2_BYTES / 1e6:.0f} MB L2",
         },
@@ -867,7 +867,7 @@ def run_gemm_leg(job: Job, w: dict, name: str, launches: int = REF_LAUNCHES, dro
             "sm_mhz_in_kernel": mhz,
             "plan": {"tile": [res.tile_m, res.tile_n, res.tile_k], "stages": res.stages, "grid_ctas": res.grid_ctas, "cta_group": res.cta_group,
                      "tail_split": [res.tail_tiles, res.tail_parts], "tail_exchange": res.tail_exchange, "b_layout": case.plan.b_layout,
-                     "operand_sets": case.n_sets, "l2_eviction_hints": bool(res.l2_hints)},
+                     "operand_sets": case.n_sets},
             "gpu_launches": n_launched,
             "verified": job.all_ranks_true(check["ok"]), "verify": check,
         }
@@ -909,8 +909,7 @@ def run_strong(job: Job) -> dict:
             "back_to_back_ms_per_step": ms_b2b / 20, "back_to_back_tflops_total": total_flops / (ms_b2b / 20 * 1e-3) / 1e12,
             "roofline": roofline_of(case, p50, sustained=False, sm_mhz=mhz or None),
             "per_rank_p50_ms": job.gather_floats(stats["p50_ms"]), "per_rank_sm_mhz_in_kernel": job.gather_floats(mhz),
-            "plan": {"tile": [res.tile_m, res.tile_n, res.tile_k], "stages": res.stages, "grid_ctas": res.grid_ctas, "cta_group": res.cta_group,
-                     "l2_eviction_hints": bool(res.l2_hints)},
+            "plan": {"tile": [res.tile_m, res.tile_n, res.tile_k], "stages": res.stages, "grid_ctas": res.grid_ctas, "cta_group": res.cta_group},
             "scaling_note": "efficiency at g GPUs = T_1 / (g * T_g) with T = ms_per_step of the runs at 1 and g GPUs",
             "verified": job.all_ranks_true(check["ok"]), "verify": check,
         }

@@ -178,10 +178,7 @@ typedef struct b200_gemm_resources {
    * in one round: the parts of a tile are the CTAs of one cluster; needs no workspace and is
    * always on; reserved[1] bit 2 of the description asks for the workspace form instead). */
   int32_t tail_exchange;
-  /* 1 = A, B and C together exceed the L2, and the plan runs CTA pairs: A is loaded with the
-   * evict-last priority, B with evict-first, and C is stored evict-first.  Decided from the
-   * device's L2 size at the first launch (126 MiB assumed before that). */
-  int32_t l2_hints;
+  int32_t reserved0;
 } b200_gemm_resources;
 
 typedef struct b200_gemm_plan b200_gemm_plan;

@@ -112,12 +112,7 @@ def test_plan_resources_without_a_gpu(native_lib):
     # 34 tiles x 2 parts: fp32 partial tiles of 256 x 256 plus one ready flag per epilogue warp, padded to 256 bytes
     assert (r.tail_tiles, r.tail_parts) == (34, 2)
     assert r.optional_workspace_bytes == 34 * 2 * 256 * 256 * 4 + -(-(34 * 2 * 2 * 4 * 4) // 256) * 256
-    big = GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources()
-    assert big.tail_parts == 0
-    # eviction priorities in the L2: only CTA-pair plans whose A + B + C exceed it (96 MiB here, 384 MiB there)
-    assert (r.l2_hints, big.l2_hints, single.l2_hints) == (0, 1, 0)
-    assert GemmPlan(8192, 8192, 2048, "bf16", "bf16").resources().l2_hints == 1  # 32 + 32 + 128 MiB
-    assert GemmPlan(8192, 8192, 8192, "bf16", "bf16", cta_group=1).resources().l2_hints == 0
+    assert GemmPlan(8192, 8192, 8192, "bf16", "bf16").resources().tail_parts == 0
     fp8 = GemmPlan(256, 256, 1024, "e4m3", "bf16").resources()
     assert fp8.tile_k == 128
     skinny = GemmPlan(16, 8192, 8192, "bf16", "bf16", split_k=-1, tile_n=64).resources()
