@@ -893,7 +893,14 @@ def run_strong(job: Job) -> dict:
             case.run_step(i)
         nat.call("b200_device_synchronize")
         job.barrier()
+        sampler = ClockSampler(job.local_rank)
+        sampler.start()
+        t0 = time.perf_counter()
         stats = time_reference_protocol(case.run_step, 60, 10, plan=case.plan)
+        t1 = time.perf_counter()
+        clocks = sampler.summary(t0, t1)
+        sampler.stop()
+        inside = [s[1] for s in sampler.samples if t0 <= s[0] <= t1]
         case.plan.status()
         mhz = stats["sm_mhz"]
         ms_b2b, _, _, _ = time_steps(job, case.run_step, 20, 3)
@@ -913,6 +920,13 @@ def run_strong(job: Job) -> dict:
             "scaling_note": "efficiency at g GPUs = T_1 / (g * T_g) with T = ms_per_step of the runs at 1 and g GPUs",
             "verified": job.all_ranks_true(check["ok"]), "verify": check,
         }
+        leg["clocks"] = clocks
+        if inside:
+            # The in-kernel clock is that of the one SM that runs CTA 0; NVML's samples of the
+            # region are the second opinion (rank 0's GPU).
+            med = float(np.median(inside))
+            leg["nvml_sm_mhz_median"] = med
+            leg["frac_of_nvml_clock_peak"] = leg["tflops_per_gpu"] / (SM_COUNT * FLOP_PER_CLK_PER_SM[2] * med * 1e6 / 1e12)
         if job.dist is not None and job.world > 1:
             leg["allgather"] = time_allgather(job, case.sets[0][2], case.rows, case.N)
         return leg
