@@ -613,6 +613,7 @@ def roofline_of(case: GemmCase, ms: float, sustained: bool, sm_mhz: float | None
         clock_peak = SM_COUNT * FLOP_PER_CLK_PER_SM[1 if eight else 2] * sm_mhz * 1e6 / 1e12
         out["sm_mhz_in_kernel"] = sm_mhz  # SM cycles / nanoseconds counted by the timed launches themselves
         out["frac_of_clock_peak"] = achieved / clock_peak
+        out["clock_note"] = "clock of the SM that ran CTA 0; the SMs of one launch differ by up to 4 %, so can the fraction"
     return out
 
 
