@@ -923,11 +923,10 @@ def run_strong(job: Job) -> dict:
         }
         leg["clocks"] = clocks
         if inside:
-            # The in-kernel clock is that of the one SM that runs CTA 0; NVML's samples of the
-            # region are the second opinion (rank 0's GPU).
-            med = float(np.median(inside))
-            leg["nvml_sm_mhz_median"] = med
-            leg["frac_of_nvml_clock_peak"] = leg["tflops_per_gpu"] / (SM_COUNT * FLOP_PER_CLK_PER_SM[2] * med * 1e6 / 1e12)
+            # The in-kernel clock is that of the one SM that runs CTA 0.  NVML's samples of the region
+            # (rank 0's GPU) are printed beside it as they are: the launches are synchronised one by
+            # one, so some samples fall between two launches, where the clock is back at its maximum.
+            leg["nvml_sm_mhz_quartiles"] = [float(np.percentile(inside, q)) for q in (0, 25, 50, 75, 100)]
         if job.dist is not None and job.world > 1:
             leg["allgather"] = time_allgather(job, case.sets[0][2], case.rows, case.N)
         return leg
