@@ -271,8 +271,9 @@ int b200_gemm_splitk_noalloc_status(uint32_t words[4]);
 int b200_vector_add_i32(const int32_t* a, const int32_t* b, int32_t* c, size_t n, void* stream);
 int b200_vector_add_f32(const float* a, const float* b, float* c, size_t n, void* stream);
 /* dst[M,N] = src[M,N], fp32 row-major, N % 4 == 0; elements outside MxN are not touched.
- * `depth` (1..8) = 16-byte loads in flight per thread, `num_ctas` = persistent grid size
- * (0 = a multiple of the SM count).  examples/06_copy_layout/copy_2d_padded.py:34-151. */
+ * `depth` (1..8) = 16-byte loads in flight per thread, `num_ctas` = grid size over which the
+ * chunks are dealt (0 = one CTA per chunk, at most 512 per SM, which is the fastest).
+ * examples/06_copy_layout/copy_2d_padded.py:34-151. */
 int b200_copy_2d_padded_f32(const float* src, float* dst, int64_t M, int64_t N, int depth,
                             int num_ctas, void* stream);
 /* out[i] = max(a[i] + b[i], 0); examples/07_simple_fusion/simple_fusion.py:62-144. */
