@@ -156,8 +156,14 @@ __host__ __device__ constexpr int stage_bytes(int bn, int cg = 1, bool mx = fals
 // 128-row A read runs into): full[16], empty[16], acc_full[2], acc_empty[2], drain, TMEM base
 // slot, abort flag, and one barrier per epilogue warp for the cluster exchange.
 constexpr int kBarrierBytes = 384;
+// Bytes behind the last stage that the MMA's 128-row read of a short A tile still touches: the
+// read covers 16 KB from the stage's start, i.e. the stage's own B tile first, and only runs past
+// the stage when A and B together are shorter than that (32 rows of A with a 64-column tile).
+__host__ __device__ constexpr int a_overrun_bytes(int bn, int cg = 1, bool mx = false, int am = kBM) {
+  return kBM * kRowBytes > stage_bytes(bn, cg, mx, am) ? kBM * kRowBytes - stage_bytes(bn, cg, mx, am) : 0;
+}
 __host__ __device__ constexpr int smem_bytes(int bn, int stages, int cg = 1, bool mx = false, int am = kBM) {
-  return stages * stage_bytes(bn, cg, mx, am) + (kBM - am) * kRowBytes + kBarrierBytes + 1024;
+  return stages * stage_bytes(bn, cg, mx, am) + a_overrun_bytes(bn, cg, mx, am) + kBarrierBytes + 1024;
 }
 // Two accumulators of bn columns; a block-scaled kernel adds two sets of 16 scale columns.
 constexpr int kScaleTmemCols = 16;
@@ -445,7 +451,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_raw_u32 = smem_u32(smem_raw);
   const uint32_t smem_base = (smem_raw_u32 + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-  const uint32_t bar_base = smem_base + static_cast<uint32_t>(p.stages) * kStageBytes + (kBM - AM) * kRowBytes;
+  const uint32_t bar_base = smem_base + static_cast<uint32_t>(p.stages) * kStageBytes + a_overrun_bytes(BN, CG, MX, AM);
   uint8_t* bar_ptr = smem_raw + (bar_base - smem_raw_u32);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 128u + 8u * s; };

@@ -64,7 +64,7 @@ struct Variant {
 };
 constexpr int kMaxSmemOptin = 232448;  // 227 KB: the sm_100 per-block opt-in limit
 constexpr int stages_short_a(int am) {  // as many short-A stages as fit, up to the ring's maximum
-  const int fit = (kMaxSmemOptin - gemm::kBarrierBytes - 1024 - (gemm::kBM - am) * gemm::kRowBytes) / gemm::stage_bytes(kTileN, 1, false, am);
+  const int fit = (kMaxSmemOptin - gemm::kBarrierBytes - 1024 - gemm::a_overrun_bytes(kTileN, 1, false, am)) / gemm::stage_bytes(kTileN, 1, false, am);
   return fit < gemm::kMaxStages ? fit : gemm::kMaxStages;
 }
 Variant variant_for(int64_t M, bool f32) {

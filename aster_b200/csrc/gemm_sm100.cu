@@ -784,8 +784,14 @@ int b200_gemm_plan_create(const b200_gemm_desc* desc, b200_gemm_plan** out) {
   int am = gemm::kBM;
   if (cg == 1 && !mx && d.tile_m == 0 && d.M <= 64 && (bn == 64 || bn == 128)) am = d.M <= 32 ? 32 : 64;
   plan->am = am;
-  const int stage_cap = am < gemm::kBM ? gemm::kMaxStages : 8;  // full-A stages never profit from more than 8 slots
-  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024 - (gemm::kBM - am) * gemm::kRowBytes) / gemm::stage_bytes(bn, cg, mx, am);
+  // Full-A stages never profit from more than 8 slots.  Short-A stages belong to problems that
+  // stream B from HBM, and a stream of 16 KB copies is fastest with about 100 KB per SM on request
+  // (a copy-only probe over 128 SMs: 6.9 / 7.1 / 6.5 TB/s with 64 / 96 / 160 KB in flight; the
+  // M = 16, N = K = 8192 launch: 27.1 / 27.5 / 27.9 us with 6 / 10 / 11 slots): 112 KB of B tiles.
+  const int b_stage_bytes = bn / cg * gemm::kRowBytes;
+  const int short_a_cap = std::max(4, std::min(gemm::kMaxStages, (112 * 1024 + b_stage_bytes - 1) / b_stage_bytes));
+  const int stage_cap = am < gemm::kBM ? short_a_cap : 8;
+  const int max_stages = (kMaxSmemOptin - gemm::kBarrierBytes - 1024 - gemm::a_overrun_bytes(bn, cg, mx, am)) / gemm::stage_bytes(bn, cg, mx, am);
   int stages = d.stages > 0 ? d.stages : (max_stages < stage_cap ? max_stages : stage_cap);
   if (stages > max_stages) {
     delete plan;

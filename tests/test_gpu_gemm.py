@@ -754,9 +754,14 @@ class TestSkinnyM:
             b.free()
 
     def test_deep_rings_and_other_types(self, gpu):
+        # short A stages: as many slots as put 112 KB of B tiles on request (14 of 8 KB, 7 of 16 KB), 16 on demand
         plan = GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64)
-        assert plan.resources().stages == 16 and GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64, tile_m=128).resources().stages <= 8
+        assert plan.resources().stages == 14 and GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64, tile_m=128).resources().stages <= 8
+        assert GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=128).resources().stages == 7
+        assert GemmPlan(16, 8192, 8192, "bf16", "bf16", tile_n=64, stages=16).resources().stages == 16
         run(16, 2048, 8192, "bf16", "f32", "uniform", 4, tile_n=64, bias=True, relu=True)
+        run(16, 2048, 8192, "bf16", "f32", "uniform", 4, tile_n=64, stages=16)
+        run(16, 1024, 8192, "bf16", "bf16", "uniform", 4, tile_n=128, stages=11)  # the deepest ring of 20 KB stages
         run(24, 1000, 2064, "f16", "f32", "normal", 5, tile_n=64)            # ragged N, K not a multiple of the stage
         run(40, 512, 4096, "e4m3", "bf16", "normal", 3, tile_n=128)
         ia = np.random.default_rng(1).integers(-128, 128, (16, 2048), dtype=np.int8)
