@@ -137,8 +137,8 @@ typedef struct b200_gemm_desc {
                       * 128 asks for full A stages                                              */
   int32_t tile_n;    /* CTA tile columns: 64, 128 or 256; 0 = choose                            */
   int32_t tile_k;    /* elements per pipeline stage along K; 0 = 128 bytes' worth               */
-  int32_t stages;    /* shared-memory ring depth (<= 16); 0 = as many as fit, up to 8 (16 with
-                      * short A stages)                                                         */
+  int32_t stages;    /* shared-memory ring depth (<= 16); 0 = as many as fit, up to 8; with short
+                      * A stages as many as keep 112 KB of B tiles on request (7 of 16 KB)      */
   int32_t cta_group; /* 1 or 2 CTAs per MMA; 0 = choose                                         */
   int32_t split_k;   /* K partitions reduced through an fp32 workspace; 0/1 = none, -1 = choose */
   int32_t max_ctas;  /* persistent grid size cap; 0 = number of SMs                             */
